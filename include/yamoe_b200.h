@@ -1,0 +1,128 @@
+/*
+ * yamoe_b200 — C ABI of the B200 (sm_100a) expert forward / backward library.
+ *
+ * Plain pointers and sizes only: no torch types cross this boundary.  Every pointer is a
+ * device pointer unless stated otherwise.  The library never allocates or frees device
+ * memory (all scratch comes from the caller-provided workspace, 256-byte aligned), never
+ * keeps a pointer after a call returns, performs no host/device synchronisation and
+ * enqueues all work on the stream it is given.
+ *
+ * Every entry point returns YAMOE_OK (0) or a negative yamoe_status_t.
+ *
+ * The comments cite the interface of the reference project (drbh/yamoe) that each entry
+ * point replaces, as path:line within that project.
+ */
+#ifndef YAMOE_B200_H_
+#define YAMOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  YAMOE_OK = 0,
+  YAMOE_ERR_BAD_ARG = -1,        /* null pointer, non-positive size, H not a multiple of 8, ... */
+  YAMOE_ERR_WORKSPACE = -2,      /* workspace pointer null / misaligned / too small          */
+  YAMOE_ERR_DTYPE = -3,          /* dtype is not YAMOE_F32 or YAMOE_BF16                      */
+  YAMOE_ERR_CUDA = -4,           /* a CUDA runtime / driver call failed (launch, tensor map)  */
+  YAMOE_ERR_UNSUPPORTED = -5,    /* valid request this build cannot serve                     */
+  YAMOE_ERR_DEVICE_TIMEOUT = -6  /* a bounded device-side wait gave up (see device status)    */
+} yamoe_status_t;
+
+typedef enum { YAMOE_F32 = 0, YAMOE_BF16 = 1 } yamoe_dtype_t;
+
+/* Path selection for the GEMMs.  AUTO picks tcgen05 for bf16 when shapes allow, the GEMV path
+ * for decode-sized bf16 token counts, and the SIMT path otherwise (fp32 always). */
+typedef enum {
+  YAMOE_PATH_AUTO = 0,
+  YAMOE_PATH_SIMT = 1,     /* CUDA-core FFMA grouped GEMM, fp32 accumulate (any dtype)     */
+  YAMOE_PATH_TCGEN05 = 2,  /* tcgen05 / TMEM / TMA grouped GEMM (bf16 only)                */
+  YAMOE_PATH_GEMV = 3      /* weight-streaming GEMV path for small token counts (bf16)     */
+} yamoe_path_t;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int yamoe_b200_version(void);
+
+/* Human-readable name of a status code; never NULL. */
+const char *yamoe_b200_status_string(int status);
+
+/* Process-wide path override used by tests and the benchmark; returns the previous value. */
+int yamoe_b200_set_path(int path);
+
+/* ---------------------------------------------------------------------------------------------
+ * Routing: stable sort of the S = T*K (token, slot) assignments by expert id, per-expert
+ * histogram and inclusive prefix sum.  Replaces sort_cuda (csrc/sort.cu:61-91) and
+ * bincount_cumsum_cuda (csrc/bincount_cumsum.cu:58-98) as used at csrc/moe.cpp:141-144.
+ *
+ *   router_indices  int64 [T*K]        expert id of assignment p = t*K + slot
+ *   sorted_values   int32 [T*K]  out   expert ids in ascending order
+ *   sorted_indices  int32 [T*K]  out   flat position p of each sorted entry (ties: ascending p)
+ *   bins            int32 [E+1]  out   bins[e] = number of assignments with id <= e; bins[E] = 0
+ *   counts          int32 [E]    out   per-expert histogram (may be NULL)
+ * Bit-exact and deterministic.  Ids outside [0,E) are dropped from all outputs.
+ * ------------------------------------------------------------------------------------------- */
+size_t yamoe_b200_route_workspace_bytes(int64_t T, int E, int K);
+int yamoe_b200_route(const int64_t *router_indices, int32_t *sorted_values, int32_t *sorted_indices,
+                     int32_t *bins, int32_t *counts, int64_t T, int E, int K,
+                     void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Expert forward.  Replaces experts_cuda (csrc/moe.cpp:45-223; schema
+ * torch-ext/torch_binding.cpp:58-69).
+ *
+ *   hidden_states     dtype [T,H]
+ *   router_indices    int64 [T,K]
+ *   routing_weights   dtype [T,routing_cols], routing_cols == E (dense) or == K (per slot)
+ *   gate_up_proj      dtype [E,H,2H]   gate = even columns, up = odd columns
+ *   gate_up_proj_bias dtype [E,2H]
+ *   down_proj         dtype [E,H,H]
+ *   down_proj_bias    dtype [E,H]
+ *   out               dtype [T,H]      fully overwritten
+ *   expert_capacity   rows kept per expert: the first min(n_e, capacity) assignments of expert e
+ *                     in stable sorted order (csrc/gather.cu:18-26, csrc/scatter.cu:78-96)
+ * ------------------------------------------------------------------------------------------- */
+size_t yamoe_b200_forward_workspace_bytes(int64_t T, int H, int E, int K, int dtype);
+int yamoe_b200_experts_forward(const void *hidden_states, const int64_t *router_indices,
+                               const void *routing_weights, int routing_cols,
+                               const void *gate_up_proj, const void *gate_up_proj_bias,
+                               const void *down_proj, const void *down_proj_bias, void *out,
+                               int64_t T, int H, int E, int K, int64_t expert_capacity, int dtype,
+                               void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Expert backward.  Replaces experts_backward_cuda (csrc/experts_backward.cu:126-341; schema
+ * torch-ext/torch_binding.cpp:71-83).  Gradients are written in the order the reference
+ * returns them (csrc/experts_backward.cu:340); every output is fully overwritten.
+ *
+ *   grad_out          dtype, T*H elements, or T*K*H elements (grad_out_per_slot != 0) that are
+ *                     summed over K first (csrc/experts_backward.cu:224-228)
+ *   d_hidden          dtype [T,H]
+ *   d_routing         dtype [T,routing_cols]; zero outside selected, kept entries.  The value is
+ *                     the autograd gradient <grad_out[t], y_e[t]>; the reference applies the sort
+ *                     permutation twice here (csrc/experts_backward.cu:261-264) and is not followed.
+ *   d_gate_up_proj    dtype [E,H,2H];  d_gate_up_proj_bias dtype [E,2H]
+ *   d_down_proj       dtype [E,H,H];   d_down_proj_bias    dtype [E,H]
+ * ------------------------------------------------------------------------------------------- */
+size_t yamoe_b200_backward_workspace_bytes(int64_t T, int H, int E, int K, int dtype);
+int yamoe_b200_experts_backward(const void *grad_out, int grad_out_per_slot,
+                                const void *hidden_states, const int64_t *router_indices,
+                                const void *routing_weights, int routing_cols,
+                                const void *gate_up_proj, const void *gate_up_proj_bias,
+                                const void *down_proj, const void *down_proj_bias,
+                                void *d_hidden, void *d_routing, void *d_gate_up_proj,
+                                void *d_gate_up_proj_bias, void *d_down_proj, void *d_down_proj_bias,
+                                int64_t T, int H, int E, int K, int64_t expert_capacity, int dtype,
+                                void *workspace, size_t workspace_bytes, void *stream);
+
+/* Device status word of the last forward/backward call that used `workspace`: 0 when every
+ * bounded device-side wait completed, otherwise a code naming the wait that gave up.  Reads
+ * 4 bytes from the device with cudaMemcpyAsync on `stream` and synchronises that stream. */
+int yamoe_b200_device_status(const void *workspace, void *stream, int32_t *status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* YAMOE_B200_H_ */

@@ -1,0 +1,16 @@
+"""yamoe_b200: the expert forward/backward op of drbh/yamoe as hand-written sm_100a CUDA behind
+the reference's operator interface (torch-ext/yamoe/__init__.py:6-12)."""
+from . import _lib
+from .layers import _ExpertsFn, experts_autograd
+from .ops import bincount_cumsum, experts, experts_backward, route, sort
+
+
+def set_path(name: str) -> str:
+    """Select the GEMM path: "auto", "simt", "tcgen05" or "gemv".  Returns the previous one."""
+    names = ["auto", "simt", "tcgen05", "gemv"]
+    prev = _lib.lib().yamoe_b200_set_path(names.index(name))
+    return names[prev]
+
+
+__all__ = ["experts", "experts_backward", "sort", "bincount_cumsum", "route", "experts_autograd",
+           "_ExpertsFn", "set_path"]

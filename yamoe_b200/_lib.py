@@ -1,0 +1,56 @@
+"""ctypes view of the C ABI declared in include/yamoe_b200.h.
+
+The shared library must exist in-tree (built by `python -m yamoe_b200.build` or
+`__graft_entry__.build()`); there is no fallback of any kind: a missing library raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from .build import LIB_PATH
+
+c_void_p, c_int, c_int64, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
+
+YAMOE_F32, YAMOE_BF16 = 0, 1
+PATH_AUTO, PATH_SIMT, PATH_TCGEN05, PATH_GEMV = 0, 1, 2, 3
+
+# name -> (restype, argtypes); mirrors include/yamoe_b200.h one to one
+SIGNATURES = {
+    "yamoe_b200_version": (c_int, []),
+    "yamoe_b200_status_string": (ctypes.c_char_p, [c_int]),
+    "yamoe_b200_set_path": (c_int, [c_int]),
+    "yamoe_b200_route_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
+    "yamoe_b200_route": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_forward_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
+    "yamoe_b200_experts_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 5 +
+                                   [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_backward_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
+    "yamoe_b200_experts_backward": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int] +
+                                    [c_void_p] * 10 +
+                                    [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_device_status": (c_int, [c_void_p, c_void_p, ctypes.POINTER(ctypes.c_int32)]),
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m yamoe_b200.build`. "
+                "yamoe_b200 has no CPU or PyTorch fallback.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = lib().yamoe_b200_status_string(status).decode()
+        raise RuntimeError(f"yamoe_b200: {what} failed: {msg} (status {status})")

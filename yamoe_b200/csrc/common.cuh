@@ -1,0 +1,66 @@
+// Shared definitions for the yamoe_b200 kernels: status codes, dtype traits, small helpers.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/yamoe_b200.h"
+
+namespace yb {
+
+constexpr int kTileM = 128;          // row padding granularity of the expert-sorted buffers
+constexpr float kAlpha = 1.702f;     // reference: csrc/moe.cpp:179
+constexpr float kLimit = 7.0f;       // reference: csrc/moe.cpp:175
+
+#define YB_CUDA_OK(expr)                                  \
+  do {                                                    \
+    cudaError_t _e = (expr);                              \
+    if (_e != cudaSuccess) return YAMOE_ERR_CUDA;         \
+  } while (0)
+
+template <typename T> struct DT;
+template <> struct DT<float> {
+  static __device__ __forceinline__ float ld(const float* p) { return *p; }
+  static __device__ __forceinline__ void st(float* p, float v) { *p = v; }
+};
+template <> struct DT<__nv_bfloat16> {
+  static __device__ __forceinline__ float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+__host__ __device__ inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+__host__ __device__ inline int64_t ceil_div(int64_t x, int64_t m) { return (x + m - 1) / m; }
+
+// Upper bound on the number of kTileM-row tiles the padded, expert-sorted layout can use:
+// every expert rounds its kept rows up to a multiple of kTileM.
+inline int64_t max_row_tiles(int64_t S, int E) {
+  int64_t ne = E < S ? E : S;
+  return ceil_div(S, kTileM) + ne;
+}
+
+// Clamped SwiGLU of one (gate, up) pre-activation pair.  reference: csrc/moe.cpp:167-180.
+__device__ __forceinline__ float glu_act(float g, float u) {
+  g = fminf(g, kLimit);
+  u = fminf(fmaxf(u, -kLimit), kLimit);
+  float s = 1.0f / (1.0f + __expf(-kAlpha * g));
+  return (u + 1.0f) * (g * s);
+}
+
+// Routing tables kept at the head of every workspace (all int32 unless noted).
+struct RouteTables {
+  int32_t* header;       // [16]: 0 ticket, 1 n_row_tiles, 2 rows_used, 3 dropped, 4 device status
+  int32_t* counts;       // [E]
+  int32_t* bins;         // [E+1] inclusive prefix sums, bins[E] = 0
+  int32_t* pad_off;      // [E+1] first padded row of each expert, pad_off[E] = rows_used
+  int32_t* block_counts; // [nblk*E] per-block histogram, then exclusive prefix over blocks
+  int32_t* tile_expert;  // [max_row_tiles] expert owning each kTileM-row tile
+  int32_t* sorted_values;   // [S]
+  int32_t* sorted_indices;  // [S]
+  int32_t* row_token;    // [max_rows] token of each padded row, -1 for padding
+  int32_t* row_flat;     // [max_rows] flat position p = t*K + slot, -1 for padding
+  float* row_weight;     // [max_rows] routing weight of the row
+};
+
+enum HeaderSlot { kHdrTicket = 0, kHdrRowTiles = 1, kHdrRowsUsed = 2, kHdrDropped = 3, kHdrStatus = 4 };
+
+}  // namespace yb

@@ -1,0 +1,135 @@
+// Memory-bound helper kernels around the grouped GEMMs: row gathers into the padded,
+// expert-sorted layout, the fp32 -> storage cast of the combined output, bias-gradient column
+// sums and the placement of routing-weight gradients.
+#pragma once
+#include "common.cuh"
+#include "epilogues.cuh"
+
+namespace yb {
+
+constexpr int kRowWarps = 8;  // rows per CTA in the warp-per-row kernels
+
+// dst[row, :] = src[row_token[row], :], zeros for padding rows.  One warp per row, 16-byte
+// accesses.  reference: csrc/gather.cu:6-66 (which writes a padded [E,C,H] buffer instead).
+template <typename T>
+__global__ void __launch_bounds__(kRowWarps * 32)
+gather_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, const int32_t* __restrict__ row_token,
+                   const int32_t* __restrict__ header, int H) {
+  const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+  if (row >= header[kHdrRowsUsed]) return;
+  const int lane = threadIdx.x & 31;
+  const int tok = row_token[row];
+  const int nvec = H * (int)sizeof(T) / 16;
+  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)row * H);
+  if (tok < 0) {
+    for (int i = lane; i < nvec; i += 32) d[i] = make_uint4(0, 0, 0, 0);
+  } else {
+    const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)tok * H);
+    for (int i = lane; i < nvec; i += 32) d[i] = __ldg(s + i);
+  }
+}
+
+// Backward gather: gys[row, :] = grad_y[token, :] where grad_y is grad_out, or the sum of its K
+// slot slices (reference: csrc/experts_backward.cu:224-228); also seeds the routing-weight
+// gradient of the row with <grad_y[token], b_down[e]>, the bias part of <grad_y, y_e>
+// (reference: csrc/experts_backward.cu:83-88).
+template <typename T>
+__global__ void __launch_bounds__(kRowWarps * 32)
+gather_grad_kernel(const T* __restrict__ grad_out, int slots, const T* __restrict__ down_bias,
+                   T* __restrict__ gys, float* __restrict__ gw_row, const int32_t* __restrict__ row_token,
+                   const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ header, int H) {
+  const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+  if (row >= header[kHdrRowsUsed]) return;
+  const int lane = threadIdx.x & 31;
+  const int tok = row_token[row];
+  constexpr int VE = 16 / (int)sizeof(T);
+  const int nvec = H / VE;
+  T* d = gys + (size_t)row * H;
+  if (tok < 0) {
+    for (int i = lane; i < nvec; i += 32) reinterpret_cast<uint4*>(d)[i] = make_uint4(0, 0, 0, 0);
+    if (lane == 0) gw_row[row] = 0.f;
+    return;
+  }
+  const int e = tile_expert[row / kTileM];
+  const T* b = down_bias + (size_t)e * H;
+  float dot = 0.f;
+  for (int i = lane; i < nvec; i += 32) {
+    float g[VE], bb[VE];
+    load_vec<T, VE>(grad_out + ((size_t)tok * slots) * H + (size_t)i * VE, g);
+    for (int s = 1; s < slots; ++s) {
+      float g2[VE];
+      load_vec<T, VE>(grad_out + ((size_t)tok * slots + s) * H + (size_t)i * VE, g2);
+#pragma unroll
+      for (int j = 0; j < VE; ++j) g[j] += g2[j];
+    }
+    store_vec<T, VE>(d + (size_t)i * VE, g);
+    load_vec<T, VE>(b + (size_t)i * VE, bb);
+#pragma unroll
+    for (int j = 0; j < VE; ++j) dot += g[j] * bb[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (lane == 0) gw_row[row] = dot;
+}
+
+// out[i] = (T) acc[i]
+template <typename T>
+__global__ void cast_kernel(const float* __restrict__ acc, T* __restrict__ out, int64_t n_vec4) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n_vec4; i += stride) {
+    float4 q = __ldg(reinterpret_cast<const float4*>(acc) + i);
+    const float v[4] = {q.x, q.y, q.z, q.w};
+    store_vec<T, 4>(out + i * 4, v);
+  }
+}
+
+// dst[e, n] = sum over the kept rows r of expert e of  w_r * src[r, n]   (WEIGHTED)
+//                                                  or       src[r, n]
+// reference: csrc/experts_backward.cu:277 (down bias), :308 (gate_up bias).  fp32 accumulation.
+// grid (ceil(N / 256), E); empty experts get exact zeros.
+template <typename T, bool WEIGHTED>
+__global__ void __launch_bounds__(256)
+colsum_kernel(const T* __restrict__ src, const float* __restrict__ row_weight,
+              const int32_t* __restrict__ pad_off, const int32_t* __restrict__ counts, int64_t capacity,
+              T* __restrict__ dst, int N) {
+  const int e = blockIdx.y;
+  const int n = blockIdx.x * 256 + threadIdx.x;
+  if (n >= N) return;
+  const int r0 = pad_off[e];
+  const int c = counts[e];
+  const int kept = (int64_t)c < capacity ? c : (int)capacity;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int r = 0;
+  for (; r + 4 <= kept; r += 4) {
+    const T* p = src + (size_t)(r0 + r) * N + n;
+    float v0 = DT<T>::ld(p), v1 = DT<T>::ld(p + N), v2 = DT<T>::ld(p + 2 * (size_t)N), v3 = DT<T>::ld(p + 3 * (size_t)N);
+    if constexpr (WEIGHTED) {
+      v0 *= row_weight[r0 + r]; v1 *= row_weight[r0 + r + 1]; v2 *= row_weight[r0 + r + 2]; v3 *= row_weight[r0 + r + 3];
+    }
+    s0 += v0; s1 += v1; s2 += v2; s3 += v3;
+  }
+  for (; r < kept; ++r) {
+    float v = DT<T>::ld(src + (size_t)(r0 + r) * N + n);
+    if constexpr (WEIGHTED) v *= row_weight[r0 + r];
+    s0 += v;
+  }
+  DT<T>::st(dst + (size_t)e * N + n, (s0 + s1) + (s2 + s3));
+}
+
+// d_routing[t, e] (dense) or d_routing[t, slot] = gw_row[row] for every kept row.
+// reference: csrc/experts_backward.cu:266-274 (placement), with the sort permutation applied once.
+template <typename T>
+__global__ void routing_grad_kernel(const float* __restrict__ gw_row, const int32_t* __restrict__ row_token,
+                                    const int32_t* __restrict__ row_flat, const int32_t* __restrict__ tile_expert,
+                                    const int32_t* __restrict__ header, T* __restrict__ d_routing,
+                                    int routing_cols, int E) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= header[kHdrRowsUsed]) return;
+  const int tok = row_token[row];
+  if (tok < 0) return;
+  const size_t idx = (routing_cols == E) ? (size_t)tok * E + tile_expert[row / kTileM] : (size_t)row_flat[row];
+  DT<T>::st(d_routing + idx, gw_row[row]);
+}
+
+}  // namespace yb

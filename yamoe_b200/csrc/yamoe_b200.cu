@@ -1,0 +1,410 @@
+// C ABI of the yamoe_b200 library: argument checks, workspace carving and the sequencing of
+// the routing, gather, grouped-GEMM and reduction kernels for the expert forward and backward
+// passes.  Takes the place of the reference's orchestration in csrc/moe.cpp:45-223 and
+// csrc/experts_backward.cu:126-341; none of that code allocates here — all scratch lives in
+// the caller's workspace — and nothing synchronises with the host.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+#include "epilogues.cuh"
+#include "misc_kernels.cuh"
+#include "routing.cuh"
+#include "simt_gemm.cuh"
+#include "umma_gemm.cuh"
+#include "gemv.cuh"
+
+namespace yb {
+
+static std::atomic<int> g_path{-1};
+
+static int current_path() {
+  int p = g_path.load();
+  if (p >= 0) return p;
+  const char* env = std::getenv("YAMOE_B200_PATH");
+  p = YAMOE_PATH_AUTO;
+  if (env != nullptr) {
+    if (!std::strcmp(env, "simt")) p = YAMOE_PATH_SIMT;
+    else if (!std::strcmp(env, "tcgen05")) p = YAMOE_PATH_TCGEN05;
+    else if (!std::strcmp(env, "gemv")) p = YAMOE_PATH_GEMV;
+  }
+  g_path.store(p);
+  return p;
+}
+
+// Bump allocator over the caller's workspace; with base == nullptr it only measures.
+struct Bump {
+  char* base;
+  size_t off = 0;
+  explicit Bump(void* b) : base(reinterpret_cast<char*>(b)) {}
+  template <typename U>
+  U* take(size_t n) {
+    off = (off + 255) & ~size_t(255);
+    U* p = base ? reinterpret_cast<U*>(base + off) : nullptr;
+    off += n * sizeof(U);
+    return p;
+  }
+};
+
+struct Plan {
+  RouteTables rt;
+  int64_t S, max_rows, max_tiles;
+  size_t esize;
+  // forward
+  void* xs = nullptr;      // [max_rows, H]   gathered hidden rows
+  void* act = nullptr;     // [max_rows, H]   GLU output
+  float* acc32 = nullptr;  // [T, H]          fp32 combine target when the output is bf16
+  // backward
+  void* gys = nullptr;     // [max_rows, H]   gathered grad_y rows
+  void* pre = nullptr;     // [max_rows, 2H]  biased pre-activations
+  void* actw = nullptr;    // [max_rows, H]   routing weight * activation
+  void* gpre = nullptr;    // [max_rows, 2H]  gradient of the pre-activations
+  float* gw_row = nullptr; // [max_rows]
+  size_t bytes = 0;
+  size_t row_tables_bytes = 0;
+};
+
+static void carve_tables(Bump& b, Plan& p, int64_t T, int E, int K, bool rows) {
+  p.S = T * K;
+  p.max_tiles = max_row_tiles(p.S, E);
+  p.max_rows = p.max_tiles * kTileM;
+  p.rt.header = b.take<int32_t>(16);
+  p.rt.counts = b.take<int32_t>(E);
+  p.rt.bins = b.take<int32_t>(E + 1);
+  p.rt.pad_off = b.take<int32_t>(E + 1);
+  p.rt.block_counts = b.take<int32_t>((size_t)route_blocks(p.S) * E);
+  p.rt.tile_expert = b.take<int32_t>(p.max_tiles);
+  p.rt.sorted_values = b.take<int32_t>(p.S);
+  p.rt.sorted_indices = b.take<int32_t>(p.S);
+  if (rows) {
+    // row_token and row_flat are adjacent so that one memset marks every row as padding
+    p.rt.row_token = b.take<int32_t>(2 * (size_t)p.max_rows);
+    p.rt.row_flat = p.rt.row_token ? p.rt.row_token + p.max_rows : nullptr;
+    p.row_tables_bytes = 2 * (size_t)p.max_rows * sizeof(int32_t);
+    p.rt.row_weight = b.take<float>(p.max_rows);
+  } else {
+    p.rt.row_token = p.rt.row_flat = nullptr;
+    p.rt.row_weight = nullptr;
+  }
+}
+
+static Plan plan_forward(void* ws, int64_t T, int H, int E, int K, int dtype) {
+  Plan p;
+  Bump b(ws);
+  p.esize = dtype == YAMOE_BF16 ? 2 : 4;
+  carve_tables(b, p, T, E, K, true);
+  p.xs = b.take<char>((size_t)p.max_rows * H * p.esize);
+  p.act = b.take<char>((size_t)p.max_rows * H * p.esize);
+  if (dtype == YAMOE_BF16) p.acc32 = b.take<float>((size_t)T * H);
+  p.bytes = b.off + 256;
+  return p;
+}
+
+static Plan plan_backward(void* ws, int64_t T, int H, int E, int K, int dtype) {
+  Plan p;
+  Bump b(ws);
+  p.esize = dtype == YAMOE_BF16 ? 2 : 4;
+  carve_tables(b, p, T, E, K, true);
+  p.xs = b.take<char>((size_t)p.max_rows * H * p.esize);
+  p.gys = b.take<char>((size_t)p.max_rows * H * p.esize);
+  p.pre = b.take<char>((size_t)p.max_rows * 2 * H * p.esize);
+  p.actw = b.take<char>((size_t)p.max_rows * H * p.esize);
+  p.gpre = b.take<char>((size_t)p.max_rows * 2 * H * p.esize);
+  p.gw_row = b.take<float>(p.max_rows);
+  if (dtype == YAMOE_BF16) p.acc32 = b.take<float>((size_t)T * H);
+  p.bytes = b.off + 256;
+  return p;
+}
+
+static int check_common(int64_t T, int H, int E, int K, int dtype) {
+  if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
+  if (T < 0 || H <= 0 || E <= 0 || K <= 0) return YAMOE_ERR_BAD_ARG;
+  if (H % 8 != 0) return YAMOE_ERR_BAD_ARG;
+  if (E > 1024) return YAMOE_ERR_UNSUPPORTED;
+  if (T * K >= (int64_t)1 << 30) return YAMOE_ERR_UNSUPPORTED;
+  return YAMOE_OK;
+}
+
+static int prepare_routing(const Plan& p, cudaStream_t st) {
+  YB_CUDA_OK(cudaMemsetAsync(p.rt.header, 0, 16 * sizeof(int32_t), st));
+  if (p.rt.row_token) YB_CUDA_OK(cudaMemsetAsync(p.rt.row_token, 0xFF, p.row_tables_bytes, st));
+  return YAMOE_OK;
+}
+
+static bool use_tcgen05(int path, int dtype, int H) {
+  if (dtype != YAMOE_BF16 || !umma_available()) return false;
+  if (H % 64 != 0) return false;
+  return path == YAMOE_PATH_AUTO || path == YAMOE_PATH_TCGEN05;
+}
+
+template <typename T>
+static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw, int rcols, const void* wgu,
+                        const void* bgu, const void* wd, const void* bd, void* out, int64_t Tn, int H, int E,
+                        int K, int64_t cap, int dtype, void* ws, cudaStream_t st) {
+  Plan p = plan_forward(ws, Tn, H, E, K, dtype);
+  const int path = current_path();
+  float* acc = p.acc32 ? p.acc32 : reinterpret_cast<float*>(out);
+  YB_CUDA_OK(cudaMemsetAsync(acc, 0, (size_t)Tn * H * sizeof(float), st));
+  if (Tn == 0) return YAMOE_OK;
+
+  if (dtype == YAMOE_BF16 && (path == YAMOE_PATH_GEMV || (path == YAMOE_PATH_AUTO && gemv_preferred(Tn, E, K)))) {
+    int rc = launch_gemv_forward(hidden, ridx, rw, rcols, wgu, bgu, wd, bd, out, Tn, H, E, K, cap, p.act, acc, st);
+    if (rc != YAMOE_ERR_UNSUPPORTED) return rc;
+  }
+
+  int rc = prepare_routing(p, st);
+  if (rc) return rc;
+  rc = launch_route<T>(ridx, reinterpret_cast<const T*>(rw), rcols, Tn, E, K, cap, p.rt, st);
+  if (rc) return rc;
+  const unsigned row_blocks = (unsigned)ceil_div(p.max_rows, kRowWarps);
+  gather_rows_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const T*>(hidden),
+                                                              reinterpret_cast<T*>(p.xs), p.rt.row_token,
+                                                              p.rt.header, H);
+  EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), reinterpret_cast<T*>(p.act), nullptr, nullptr,
+                p.rt.row_token, p.rt.row_weight, H};
+  EpiScatterAdd<T, true, true> comb{reinterpret_cast<const T*>(bd), acc, p.rt.row_token, p.rt.row_weight, H};
+  GemmArgs g1{p.xs, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, E,
+              p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  GemmArgs g2{p.act, H, wd, H, (int64_t)H * H, 0, H, H, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  if (use_tcgen05(path, dtype, H)) {
+    if constexpr (sizeof(T) == 2) {
+      rc = launch_umma_gemm<kFwd>(g1, glu, p.max_rows, p.max_tiles, st);
+      if (rc) return rc;
+      rc = launch_umma_gemm<kFwd>(g2, comb, p.max_rows, p.max_tiles, st);
+      if (rc) return rc;
+    }
+  } else {
+    launch_simt_gemm<T, kFwd>(g1, glu, p.max_rows, st);
+    launch_simt_gemm<T, kFwd>(g2, comb, p.max_rows, st);
+  }
+  if (p.acc32) {
+    const int64_t nv = Tn * H / 4;
+    cast_kernel<T><<<(unsigned)std::min<int64_t>(ceil_div(nv, 256), 148 * 8), 256, 0, st>>>(
+        p.acc32, reinterpret_cast<T*>(out), nv);
+  }
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+template <typename T>
+static int backward_impl(const void* grad_out, int per_slot, const void* hidden, const int64_t* ridx,
+                         const void* rw, int rcols, const void* wgu, const void* bgu, const void* wd,
+                         const void* bd, void* d_hidden, void* d_routing, void* d_wgu, void* d_bgu, void* d_wd,
+                         void* d_bd, int64_t Tn, int H, int E, int K, int64_t cap, int dtype, void* ws,
+                         cudaStream_t st) {
+  Plan p = plan_backward(ws, Tn, H, E, K, dtype);
+  const int path = current_path();
+  const size_t es = sizeof(T);
+  float* acc = p.acc32 ? p.acc32 : reinterpret_cast<float*>(d_hidden);
+  YB_CUDA_OK(cudaMemsetAsync(acc, 0, (size_t)Tn * H * sizeof(float), st));
+  YB_CUDA_OK(cudaMemsetAsync(d_routing, 0, (size_t)Tn * rcols * es, st));
+  if (Tn == 0) {
+    YB_CUDA_OK(cudaMemsetAsync(d_wgu, 0, (size_t)E * H * 2 * H * es, st));
+    YB_CUDA_OK(cudaMemsetAsync(d_bgu, 0, (size_t)E * 2 * H * es, st));
+    YB_CUDA_OK(cudaMemsetAsync(d_wd, 0, (size_t)E * H * H * es, st));
+    YB_CUDA_OK(cudaMemsetAsync(d_bd, 0, (size_t)E * H * es, st));
+    return YAMOE_OK;
+  }
+  int rc = prepare_routing(p, st);
+  if (rc) return rc;
+  rc = launch_route<T>(ridx, reinterpret_cast<const T*>(rw), rcols, Tn, E, K, cap, p.rt, st);
+  if (rc) return rc;
+  const unsigned row_blocks = (unsigned)ceil_div(p.max_rows, kRowWarps);
+  gather_rows_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const T*>(hidden),
+                                                              reinterpret_cast<T*>(p.xs), p.rt.row_token,
+                                                              p.rt.header, H);
+  gather_grad_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(
+      reinterpret_cast<const T*>(grad_out), per_slot ? K : 1, reinterpret_cast<const T*>(bd),
+      reinterpret_cast<T*>(p.gys), p.gw_row, p.rt.row_token, p.rt.tile_expert, p.rt.header, H);
+
+  // 1. recompute: pre = xs W_gu + b_gu,  actw = w * glu(pre)
+  EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), nullptr, reinterpret_cast<T*>(p.actw),
+                reinterpret_cast<T*>(p.pre), p.rt.row_token, p.rt.row_weight, H};
+  GemmArgs g1{p.xs, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, E,
+              p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  // 2. gI' = gys W_d^T; fused GLU backward -> gpre, routing-weight gradient -> gw_row
+  EpiGluBackward<T> glub{reinterpret_cast<const T*>(p.pre), reinterpret_cast<T*>(p.gpre), p.gw_row,
+                         p.rt.row_token, p.rt.row_weight, H};
+  GemmArgs g2{p.gys, H, wd, H, (int64_t)H * H, 0, H, H, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  // 3. dW_d[e] = actw_e^T gys_e
+  EpiStore<T> st_wd{reinterpret_cast<T*>(d_wd), H, H};
+  GemmArgs g3{p.actw, H, p.gys, H, 0, H, H, 0, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  // 4. dHidden[token] += gpre W_gu^T
+  EpiScatterAdd<T, false, false> sc_dh{nullptr, acc, p.rt.row_token, p.rt.row_weight, H};
+  GemmArgs g4{p.gpre, 2 * (int64_t)H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, H, 2 * H, E,
+              p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  // 5. dW_gu[e] = xs_e^T gpre_e
+  EpiStore<T> st_wgu{reinterpret_cast<T*>(d_wgu), H, 2 * H};
+  GemmArgs g5{p.xs, H, p.gpre, 2 * (int64_t)H, 0, H, 2 * H, 0, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+
+  if (use_tcgen05(path, dtype, H)) {
+    if constexpr (sizeof(T) == 2) {
+      if ((rc = launch_umma_gemm<kFwd>(g1, glu, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma_gemm<kDgrad>(g2, glub, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma_gemm<kWgrad>(g3, st_wd, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma_gemm<kDgrad>(g4, sc_dh, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma_gemm<kWgrad>(g5, st_wgu, p.max_rows, p.max_tiles, st))) return rc;
+    }
+  } else {
+    launch_simt_gemm<T, kFwd>(g1, glu, p.max_rows, st);
+    launch_simt_gemm<T, kDgrad>(g2, glub, p.max_rows, st);
+    launch_simt_gemm<T, kWgrad>(g3, st_wd, p.max_rows, st);
+    launch_simt_gemm<T, kDgrad>(g4, sc_dh, p.max_rows, st);
+    launch_simt_gemm<T, kWgrad>(g5, st_wgu, p.max_rows, st);
+  }
+  // bias gradients and routing-weight gradients
+  colsum_kernel<T, true><<<dim3((unsigned)ceil_div(H, 256), E), 256, 0, st>>>(
+      reinterpret_cast<const T*>(p.gys), p.rt.row_weight, p.rt.pad_off, p.rt.counts, cap,
+      reinterpret_cast<T*>(d_bd), H);
+  colsum_kernel<T, false><<<dim3((unsigned)ceil_div(2 * H, 256), E), 256, 0, st>>>(
+      reinterpret_cast<const T*>(p.gpre), p.rt.row_weight, p.rt.pad_off, p.rt.counts, cap,
+      reinterpret_cast<T*>(d_bgu), 2 * H);
+  routing_grad_kernel<T><<<(unsigned)ceil_div(p.max_rows, 256), 256, 0, st>>>(
+      p.gw_row, p.rt.row_token, p.rt.row_flat, p.rt.tile_expert, p.rt.header, reinterpret_cast<T*>(d_routing),
+      rcols, E);
+  if (p.acc32) {
+    const int64_t nv = Tn * H / 4;
+    cast_kernel<T><<<(unsigned)std::min<int64_t>(ceil_div(nv, 256), 148 * 8), 256, 0, st>>>(
+        p.acc32, reinterpret_cast<T*>(d_hidden), nv);
+  }
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+}  // namespace yb
+
+using namespace yb;
+
+extern "C" {
+
+int yamoe_b200_version(void) { return 100; }
+
+const char* yamoe_b200_status_string(int s) {
+  switch (s) {
+    case YAMOE_OK: return "ok";
+    case YAMOE_ERR_BAD_ARG: return "bad argument";
+    case YAMOE_ERR_WORKSPACE: return "workspace null, misaligned or too small";
+    case YAMOE_ERR_DTYPE: return "unsupported dtype";
+    case YAMOE_ERR_CUDA: return "CUDA call failed";
+    case YAMOE_ERR_UNSUPPORTED: return "unsupported configuration";
+    case YAMOE_ERR_DEVICE_TIMEOUT: return "bounded device-side wait gave up";
+    default: return "unknown status";
+  }
+}
+
+int yamoe_b200_set_path(int path) {
+  int prev = current_path();
+  if (path >= YAMOE_PATH_AUTO && path <= YAMOE_PATH_GEMV) g_path.store(path);
+  return prev;
+}
+
+size_t yamoe_b200_route_workspace_bytes(int64_t T, int E, int K) {
+  if (T < 0 || E <= 0 || K <= 0) return 0;
+  Plan p;
+  Bump b(nullptr);
+  carve_tables(b, p, T, E, K, false);
+  return b.off + 256;
+}
+
+int yamoe_b200_route(const int64_t* router_indices, int32_t* sorted_values, int32_t* sorted_indices,
+                     int32_t* bins, int32_t* counts, int64_t T, int E, int K, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  int rc = check_common(T, 8, E, K, YAMOE_F32);
+  if (rc) return rc;
+  if (!router_indices || !sorted_values || !sorted_indices || !bins) return YAMOE_ERR_BAD_ARG;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < yamoe_b200_route_workspace_bytes(T, E, K))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  Plan p;
+  Bump b(workspace);
+  carve_tables(b, p, T, E, K, false);
+  p.rt.sorted_values = sorted_values;
+  p.rt.sorted_indices = sorted_indices;
+  p.rt.bins = bins;
+  if (counts) p.rt.counts = counts;
+  p.rt.tile_expert = nullptr;
+  YB_CUDA_OK(cudaMemsetAsync(p.rt.header, 0, 16 * sizeof(int32_t), st));
+  if (T == 0) {
+    YB_CUDA_OK(cudaMemsetAsync(bins, 0, (size_t)(E + 1) * sizeof(int32_t), st));
+    if (counts) YB_CUDA_OK(cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int32_t), st));
+    return YAMOE_OK;
+  }
+  return launch_route<float>(router_indices, nullptr, E, T, E, K, (int64_t)1 << 40, p.rt, st);
+}
+
+size_t yamoe_b200_forward_workspace_bytes(int64_t T, int H, int E, int K, int dtype) {
+  if (check_common(T, H, E, K, dtype)) return 0;
+  return plan_forward(nullptr, T, H, E, K, dtype).bytes;
+}
+
+int yamoe_b200_experts_forward(const void* hidden_states, const int64_t* router_indices,
+                               const void* routing_weights, int routing_cols, const void* gate_up_proj,
+                               const void* gate_up_proj_bias, const void* down_proj, const void* down_proj_bias,
+                               void* out, int64_t T, int H, int E, int K, int64_t expert_capacity, int dtype,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_common(T, H, E, K, dtype);
+  if (rc) return rc;
+  if (routing_cols != E && routing_cols != K) return YAMOE_ERR_BAD_ARG;
+  if (expert_capacity < 0) return YAMOE_ERR_BAD_ARG;
+  if (T > 0 && (!hidden_states || !router_indices || !routing_weights || !out)) return YAMOE_ERR_BAD_ARG;
+  if (!gate_up_proj || !gate_up_proj_bias || !down_proj || !down_proj_bias) return YAMOE_ERR_BAD_ARG;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < yamoe_b200_forward_workspace_bytes(T, H, E, K, dtype))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == YAMOE_BF16)
+    return forward_impl<__nv_bfloat16>(hidden_states, router_indices, routing_weights, routing_cols, gate_up_proj,
+                                       gate_up_proj_bias, down_proj, down_proj_bias, out, T, H, E, K,
+                                       expert_capacity, dtype, workspace, st);
+  return forward_impl<float>(hidden_states, router_indices, routing_weights, routing_cols, gate_up_proj,
+                             gate_up_proj_bias, down_proj, down_proj_bias, out, T, H, E, K, expert_capacity,
+                             dtype, workspace, st);
+}
+
+size_t yamoe_b200_backward_workspace_bytes(int64_t T, int H, int E, int K, int dtype) {
+  if (check_common(T, H, E, K, dtype)) return 0;
+  return plan_backward(nullptr, T, H, E, K, dtype).bytes;
+}
+
+int yamoe_b200_experts_backward(const void* grad_out, int grad_out_per_slot, const void* hidden_states,
+                                const int64_t* router_indices, const void* routing_weights, int routing_cols,
+                                const void* gate_up_proj, const void* gate_up_proj_bias, const void* down_proj,
+                                const void* down_proj_bias, void* d_hidden, void* d_routing, void* d_gate_up_proj,
+                                void* d_gate_up_proj_bias, void* d_down_proj, void* d_down_proj_bias, int64_t T,
+                                int H, int E, int K, int64_t expert_capacity, int dtype, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+  int rc = check_common(T, H, E, K, dtype);
+  if (rc) return rc;
+  if (routing_cols != E && routing_cols != K) return YAMOE_ERR_BAD_ARG;
+  if (expert_capacity < 0) return YAMOE_ERR_BAD_ARG;
+  if (T > 0 && (!grad_out || !hidden_states || !router_indices || !routing_weights || !d_hidden || !d_routing))
+    return YAMOE_ERR_BAD_ARG;
+  if (!gate_up_proj || !gate_up_proj_bias || !down_proj || !down_proj_bias || !d_gate_up_proj ||
+      !d_gate_up_proj_bias || !d_down_proj || !d_down_proj_bias)
+    return YAMOE_ERR_BAD_ARG;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < yamoe_b200_backward_workspace_bytes(T, H, E, K, dtype))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == YAMOE_BF16)
+    return backward_impl<__nv_bfloat16>(grad_out, grad_out_per_slot, hidden_states, router_indices,
+                                        routing_weights, routing_cols, gate_up_proj, gate_up_proj_bias, down_proj,
+                                        down_proj_bias, d_hidden, d_routing, d_gate_up_proj, d_gate_up_proj_bias,
+                                        d_down_proj, d_down_proj_bias, T, H, E, K, expert_capacity, dtype,
+                                        workspace, st);
+  return backward_impl<float>(grad_out, grad_out_per_slot, hidden_states, router_indices, routing_weights,
+                              routing_cols, gate_up_proj, gate_up_proj_bias, down_proj, down_proj_bias, d_hidden,
+                              d_routing, d_gate_up_proj, d_gate_up_proj_bias, d_down_proj, d_down_proj_bias, T, H,
+                              E, K, expert_capacity, dtype, workspace, st);
+}
+
+int yamoe_b200_device_status(const void* workspace, void* stream, int32_t* status_out) {
+  if (!workspace || !status_out) return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int32_t* header = reinterpret_cast<const int32_t*>(workspace);
+  YB_CUDA_OK(cudaMemcpyAsync(status_out, header + kHdrStatus, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  YB_CUDA_OK(cudaStreamSynchronize(st));
+  return YAMOE_OK;
+}
+
+}  // extern "C"

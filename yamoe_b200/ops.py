@@ -1,0 +1,170 @@
+"""torch operators `yamoe_b200::experts` / `experts_backward` / `sort` / `bincount_cumsum`
+with the schemas of the reference binding (torch-ext/torch_binding.cpp:31-42, 58-83),
+implemented as thin calls into the C ABI: validate, allocate the output and one workspace
+tensor with torch, pass raw pointers and torch's current stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float32: _lib.YAMOE_F32, torch.bfloat16: _lib.YAMOE_BF16}
+
+torch.library.define(
+    "yamoe_b200::experts",
+    "(Tensor hidden_states, Tensor router_indices, Tensor routing_weights, Tensor gate_up_proj, "
+    "Tensor gate_up_proj_bias, Tensor down_proj, Tensor down_proj_bias, int expert_capacity, "
+    "int num_experts, int top_k) -> Tensor")
+torch.library.define(
+    "yamoe_b200::experts_backward",
+    "(Tensor grad_out, Tensor hidden_states, Tensor router_indices, Tensor routing_weights, "
+    "Tensor gate_up_proj, Tensor gate_up_proj_bias, Tensor down_proj, Tensor down_proj_bias, "
+    "int expert_capacity, int num_experts, int top_k) -> Tensor[]")
+torch.library.define("yamoe_b200::sort", "(Tensor x, int end_bit, Tensor(a!) x_out, Tensor(b!) iota_out) -> ()")
+torch.library.define("yamoe_b200::bincount_cumsum", "(Tensor input, Tensor(a!) output, int minlength) -> ()")
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _validate(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias, down_proj,
+              down_proj_bias, num_experts, top_k):
+    """Same preconditions, in the same order, as csrc/moe.cpp:58-96."""
+    names = ["hidden_states", "router_indices", "routing_weights", "gate_up_proj", "gate_up_proj_bias",
+             "down_proj", "down_proj_bias"]
+    tensors = [hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias, down_proj,
+               down_proj_bias]
+    for n, t in zip(names, tensors):
+        _require(t.is_cuda, f"{n} must be on CUDA")
+    _require(hidden_states.dim() == 2, "hidden_states must be 2D [T, H]")
+    _require(router_indices.dim() == 2, "router_indices must be 2D [T, K]")
+    _require(routing_weights.dim() == 2, "routing_weights must be 2D [T, K]")
+    _require(gate_up_proj.dim() == 3, "gate_up_proj must be 3D [E, H, 2*H]")
+    _require(gate_up_proj_bias.dim() == 2, "gate_up_proj_bias must be 2D [E, 2*H]")
+    _require(down_proj.dim() == 3, "down_proj must be 3D [E, H, H]")
+    _require(down_proj_bias.dim() == 2, "down_proj_bias must be 2D [E, H]")
+    T, H = hidden_states.shape
+    E, K = int(num_experts), int(top_k)
+    _require(tuple(router_indices.shape) == (T, K), "router_indices must be [T, K]")
+    _require(routing_weights.shape[0] == T and routing_weights.shape[1] in (K, E),
+             "routing_weights must be [T, K] or [T, E]")
+    _require(tuple(gate_up_proj.shape) == (E, H, 2 * H), "gate_up_proj must be [E, H, 2*H]")
+    _require(tuple(gate_up_proj_bias.shape) == (E, 2 * H), "gate_up_proj_bias must be [E, 2*H]")
+    _require(tuple(down_proj.shape) == (E, H, H), "down_proj must be [E, H, H]")
+    _require(tuple(down_proj_bias.shape) == (E, H), "down_proj_bias must be [E, H]")
+    dt = hidden_states.dtype
+    _require(dt in _DT, f"yamoe_b200 supports float32 and bfloat16, got {dt}")
+    for n, t in zip(names[2:], tensors[2:]):
+        _require(t.dtype == dt, f"{n} must have the dtype of hidden_states ({dt}), got {t.dtype}")
+    _require(router_indices.dtype in (torch.int64, torch.int32), "router_indices must be int64")
+    return T, H, E, K
+
+
+@torch.library.impl("yamoe_b200::experts", "CUDA")
+def _experts_cuda(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias, down_proj,
+                  down_proj_bias, expert_capacity, num_experts, top_k):
+    T, H, E, K = _validate(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias,
+                           down_proj, down_proj_bias, num_experts, top_k)
+    L = _lib.lib()
+    with torch.cuda.device(hidden_states.device):
+        hs = hidden_states.contiguous()
+        ri = router_indices.to(torch.int64).contiguous()
+        rw = routing_weights.contiguous()
+        wgu, bgu = gate_up_proj.contiguous(), gate_up_proj_bias.contiguous()
+        wd, bd = down_proj.contiguous(), down_proj_bias.contiguous()
+        out = torch.empty_like(hs)
+        dt = _DT[hs.dtype]
+        nbytes = L.yamoe_b200_forward_workspace_bytes(T, H, E, K, dt)
+        _require(nbytes > 0, "yamoe_b200: unsupported shape (H must be a positive multiple of 8, E <= 1024)")
+        ws = _workspace(nbytes, hs.device)
+        st = L.yamoe_b200_experts_forward(hs.data_ptr(), ri.data_ptr(), rw.data_ptr(), rw.shape[1], wgu.data_ptr(),
+                                          bgu.data_ptr(), wd.data_ptr(), bd.data_ptr(), out.data_ptr(), T, H, E, K,
+                                          int(expert_capacity), dt, ws.data_ptr(), ws.numel(), _stream())
+        _lib.check(st, "experts")
+    return out
+
+
+@torch.library.impl("yamoe_b200::experts_backward", "CUDA")
+def _experts_backward_cuda(grad_out, hidden_states, router_indices, routing_weights, gate_up_proj,
+                           gate_up_proj_bias, down_proj, down_proj_bias, expert_capacity, num_experts, top_k):
+    _require(grad_out.is_cuda, "grad_out must be CUDA")
+    T, H, E, K = _validate(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias,
+                           down_proj, down_proj_bias, num_experts, top_k)
+    _require(grad_out.numel() in (T * H, T * K * H), "grad_out numel must be T*H or T*K*H")
+    _require(grad_out.dtype == hidden_states.dtype, "grad_out must have the dtype of hidden_states")
+    per_slot = int(grad_out.numel() == T * K * H and K != 1)
+    L = _lib.lib()
+    with torch.cuda.device(hidden_states.device):
+        go = grad_out.contiguous()
+        hs = hidden_states.contiguous()
+        ri = router_indices.to(torch.int64).contiguous()
+        rw = routing_weights.contiguous()
+        wgu, bgu = gate_up_proj.contiguous(), gate_up_proj_bias.contiguous()
+        wd, bd = down_proj.contiguous(), down_proj_bias.contiguous()
+        d_hidden, d_routing = torch.empty_like(hs), torch.empty_like(rw)
+        d_wgu, d_bgu = torch.empty_like(wgu), torch.empty_like(bgu)
+        d_wd, d_bd = torch.empty_like(wd), torch.empty_like(bd)
+        dt = _DT[hs.dtype]
+        nbytes = L.yamoe_b200_backward_workspace_bytes(T, H, E, K, dt)
+        _require(nbytes > 0, "yamoe_b200: unsupported shape (H must be a positive multiple of 8, E <= 1024)")
+        ws = _workspace(nbytes, hs.device)
+        st = L.yamoe_b200_experts_backward(go.data_ptr(), per_slot, hs.data_ptr(), ri.data_ptr(), rw.data_ptr(),
+                                           rw.shape[1], wgu.data_ptr(), bgu.data_ptr(), wd.data_ptr(), bd.data_ptr(),
+                                           d_hidden.data_ptr(), d_routing.data_ptr(), d_wgu.data_ptr(),
+                                           d_bgu.data_ptr(), d_wd.data_ptr(), d_bd.data_ptr(), T, H, E, K,
+                                           int(expert_capacity), dt, ws.data_ptr(), ws.numel(), _stream())
+        _lib.check(st, "experts_backward")
+    return [d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd]
+
+
+def route(router_indices: torch.Tensor, num_experts: int):
+    """Stable sort of the flattened assignments by expert id plus histogram and inclusive
+    prefix sums: (sorted_values, sorted_indices, bins[E+1], counts[E]), all int32."""
+    _require(router_indices.is_cuda, "router_indices must be on CUDA")
+    flat = router_indices.to(torch.int64).contiguous().view(-1)
+    S, E = flat.numel(), int(num_experts)
+    L = _lib.lib()
+    with torch.cuda.device(flat.device):
+        opts = dict(dtype=torch.int32, device=flat.device)
+        sv, si = torch.empty(S, **opts), torch.empty(S, **opts)
+        bins, counts = torch.empty(E + 1, **opts), torch.empty(E, **opts)
+        ws = _workspace(L.yamoe_b200_route_workspace_bytes(S, E, 1), flat.device)
+        st = L.yamoe_b200_route(flat.data_ptr(), sv.data_ptr(), si.data_ptr(), bins.data_ptr(), counts.data_ptr(),
+                                S, E, 1, ws.data_ptr(), ws.numel(), _stream())
+        _lib.check(st, "route")
+    return sv, si, bins, counts
+
+
+@torch.library.impl("yamoe_b200::sort", "CUDA")
+def _sort_cuda(x, end_bit, x_out, iota_out):
+    """reference: csrc/sort.cu:61-91.  Keys must lie in [0, 2**end_bit) with 2**end_bit <= 1024
+    or simply below 1024: the counting sort serves expert ids, not general integers."""
+    _require(x.dim() == 1 and x_out.shape == x.shape and iota_out.shape == x.shape, "sort: shape mismatch")
+    sv, si, _, _ = route(x, 1024 if end_bit >= 10 else (1 << max(int(end_bit), 0)))
+    x_out.copy_(sv)
+    iota_out.copy_(si)
+
+
+@torch.library.impl("yamoe_b200::bincount_cumsum", "CUDA")
+def _bincount_cumsum_cuda(input, output, minlength):
+    """reference: csrc/bincount_cumsum.cu:58-98: output[e] = inclusive prefix sum, output[minlength:] = 0."""
+    _, _, bins, _ = route(input, int(minlength))
+    output.zero_()
+    output[:minlength].copy_(bins[:minlength])
+
+
+experts = torch.ops.yamoe_b200.experts
+experts_backward = torch.ops.yamoe_b200.experts_backward
+sort = torch.ops.yamoe_b200.sort
+bincount_cumsum = torch.ops.yamoe_b200.bincount_cumsum
