@@ -117,6 +117,20 @@ int yamoe_b200_experts_backward(const void *grad_out, int grad_out_per_slot,
                                 int64_t T, int H, int E, int K, int64_t expert_capacity, int dtype,
                                 void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Batched per-expert matmul on a uniform layout (expert e owns rows [e*C, (e+1)*C) of x).
+ * Replaces batch_mm (csrc/batch_mm.cu:7-31; schema torch-ext/torch_binding.cpp:50-56), and
+ * unlike it honours the transposed-weight flag.  `mode`:
+ *   0  out[e] [C,N] = x[e] [C,K] @ weights[e] [K,N]
+ *   1  out[e] [C,N] = x[e] [C,K] @ weights[e]^T,  weights [E,N,K]          (trans_b)
+ *   2  out[e] [M,N] = x[e]^T @ weights[e],  x [E,C,M], weights [E,C,N]     (weight gradient)
+ * C must be a multiple of 128 and N, K (M for mode 2) multiples of 64.  fp32 accumulation,
+ * output in `dtype`.
+ * ------------------------------------------------------------------------------------------- */
+size_t yamoe_b200_batch_mm_workspace_bytes(int E, int C);
+int yamoe_b200_batch_mm(const void *x, const void *weights, void *out, int E, int C, int M, int N, int K,
+                        int mode, int dtype, void *workspace, size_t workspace_bytes, void *stream);
+
 /* Device status word of the last forward/backward call that used `workspace`: 0 when every
  * bounded device-side wait completed, otherwise a code naming the wait that gave up.  Reads
  * 4 bytes from the device with cudaMemcpyAsync on `stream` and synchronises that stream. */

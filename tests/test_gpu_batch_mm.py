@@ -1,0 +1,55 @@
+"""The grouped-GEMM kernels in isolation (batched matmul sub-operator) against torch fp32
+matmuls of the same bf16-rounded operands, for each operand arrangement and both GEMM paths."""
+import pytest
+import torch
+
+from oracle import experts_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed, dtype):
+    return (torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * 0.25).to(dtype)
+
+
+@pytest.mark.parametrize("path", ["simt", "auto"])
+@pytest.mark.parametrize("E,C,K,N", [(1, 128, 64, 64), (2, 128, 128, 192), (3, 256, 320, 448), (4, 128, 64, 576)])
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_batch_mm_rows(path, E, C, K, N, trans_b):
+    import yamoe_b200
+    x = _rand((E, C, K), 1, torch.bfloat16)
+    w = _rand((E, N, K) if trans_b else (E, K, N), 2, torch.bfloat16)
+    out = torch.empty(E, C, N, dtype=torch.bfloat16, device="cuda")
+    yamoe_b200.set_path(path)
+    try:
+        yamoe_b200.batch_mm(x.cuda(), w.cuda(), torch.empty(0, device="cuda"), out, trans_b)
+        torch.cuda.synchronize()
+    finally:
+        yamoe_b200.set_path("auto")
+    ref = torch.bmm(x.float(), w.float().transpose(1, 2) if trans_b else w.float())
+    orc.check_close(out.float().cpu(), ref, 1e-2, f"batch_mm trans_b={trans_b} {path}")
+
+
+@pytest.mark.parametrize("path", ["simt", "auto"])
+@pytest.mark.parametrize("E,C,M,N", [(1, 128, 64, 64), (2, 256, 128, 192), (3, 128, 320, 448)])
+def test_batch_mm_wgrad(path, E, C, M, N):
+    import yamoe_b200
+    x = _rand((E, C, M), 3, torch.bfloat16)
+    y = _rand((E, C, N), 4, torch.bfloat16)
+    yamoe_b200.set_path(path)
+    try:
+        out = yamoe_b200.batch_mm_wgrad(x.cuda(), y.cuda())
+        torch.cuda.synchronize()
+    finally:
+        yamoe_b200.set_path("auto")
+    ref = torch.bmm(x.float().transpose(1, 2), y.float())
+    orc.check_close(out.float().cpu(), ref, 1e-2, f"batch_mm wgrad {path}")
+
+
+def test_batch_mm_fp32():
+    import yamoe_b200
+    x = _rand((2, 128, 64), 5, torch.float32)
+    w = _rand((2, 64, 128), 6, torch.float32)
+    out = torch.empty(2, 128, 128, device="cuda")
+    yamoe_b200.batch_mm(x.cuda(), w.cuda(), torch.empty(0, device="cuda"), out, False)
+    orc.check_close(out.cpu(), torch.bmm(x, w), 1e-5, "batch_mm fp32")

@@ -2,7 +2,7 @@
 the reference's operator interface (torch-ext/yamoe/__init__.py:6-12)."""
 from . import _lib
 from .layers import _ExpertsFn, experts_autograd
-from .ops import bincount_cumsum, experts, experts_backward, route, sort
+from .ops import batch_mm, batch_mm_wgrad, bincount_cumsum, experts, experts_backward, route, sort
 
 
 def set_path(name: str) -> str:
@@ -12,5 +12,5 @@ def set_path(name: str) -> str:
     return names[prev]
 
 
-__all__ = ["experts", "experts_backward", "sort", "bincount_cumsum", "route", "experts_autograd",
+__all__ = ["experts", "experts_backward", "sort", "bincount_cumsum", "route", "batch_mm", "batch_mm_wgrad", "experts_autograd",
            "_ExpertsFn", "set_path"]

@@ -251,4 +251,16 @@ struct EpiStore {
   }
 };
 
+// ---- plain store of row-tiled output C[row, n0..] (batched matmul sub-operator) --------------
+template <typename T>
+struct EpiStoreRows {
+  T* C;                      // [rows, N]
+  int N;
+
+  template <int NV>
+  __device__ __forceinline__ void apply(int /*e*/, int row, int n0, const float (&v)[NV]) const {
+    store_vec<T, NV>(C + (size_t)row * N + n0, v);
+  }
+};
+
 }  // namespace yb

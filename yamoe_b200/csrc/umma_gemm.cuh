@@ -1,8 +1,452 @@
-// placeholder until the tcgen05 kernels land
+// tcgen05 / TMEM / TMA grouped GEMM for bf16 operands with fp32 accumulation (sm_100a).
+//
+// One persistent, warp-specialised kernel serves the five GEMMs of the expert forward and
+// backward passes (the reference runs them as padded cuBLAS bmm calls: csrc/batch_mm.cu:27-30,
+// csrc/experts_backward.cu:181,198,279-282,309-311).  Arrangements (see simt_gemm.cuh):
+//   kFwd    A rows K-major (TMA 2D),           B = W[e][k][n]  MN-major (TMA 3D)
+//   kDgrad  A rows K-major (TMA 2D),           B = W[e][n][k]  K-major  (TMA 3D)
+//   kWgrad  A = act[r][m] MN-major (TMA 2D),   B = grad[r][n]  MN-major (TMA 2D), k = rows of e
+//
+// CTA = 6 warps: warp 0 issues TMA loads into a 5-stage shared-memory ring (128-byte swizzle),
+// warp 1 allocates TMEM and issues tcgen05.mma (128 x BN x 16 per instruction, one elected
+// thread), warps 2..5 drain the fp32 accumulator from TMEM with tcgen05.ld and run the epilogue
+// functor.  Two accumulators (2 x 256 TMEM columns) let the epilogue of tile i overlap the
+// main loop of tile i+1.  Tiles are walked expert by expert with the row tile varying fastest,
+// so the CTAs running at any moment share one expert's weight slab in L2.
+//
+// Every mbarrier wait is bounded: after kWaitLimitNs the waiting role raises an abort flag,
+// all roles leave their loops, the CTA frees its TMEM, records a status code in the workspace
+// header and returns.
 #pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+#include "epilogues.cuh"
 #include "simt_gemm.cuh"
+
 namespace yb {
-inline bool umma_available() { return false; }
-template <int MODE, class Epi>
-inline int launch_umma_gemm(const GemmArgs&, const Epi&, int64_t, int64_t, cudaStream_t) { return YAMOE_ERR_UNSUPPORTED; }
+
+constexpr int kUmmaBM = 128;
+constexpr int kUmmaBK = 64;            // 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaStages = 5;
+constexpr int kUmmaThreads = 192;
+constexpr int kUmmaAccStride = 256;    // TMEM columns between the two accumulators
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+enum DeviceStatus { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusMmaTimeout = 2, kStatusEpilogueTimeout = 3 };
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait on an mbarrier phase.  Returns false when the wait was abandoned.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (*abort_flag != 0 || now - t0 > kWaitLimitNs) return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor (tcgen05 format): start address, leading / stride byte
+// offsets in 16-byte units, descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+  return d;
+}
+
+struct UmmaParams {
+  int M, N, K, E;           // as GemmArgs
+  const int32_t* tile_expert;
+  const int32_t* pad_off;
+  int32_t* header;
+};
+
+template <int BN>
+struct UmmaSmem {
+  static constexpr int kABytes = kUmmaBM * 128;
+  static constexpr int kBBytes = BN * 128;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTotal = kUmmaStages * kStageBytes + 1024;   // + slack for 1024-byte alignment
+};
+
+template <int MODE, int BN, class Epi>
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const UmmaParams p, const Epi epi) {
+  using SM = UmmaSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kUmmaStages];
+  __shared__ __align__(8) uint64_t bar_empty[kUmmaStages];
+  __shared__ __align__(8) uint64_t bar_tmem_full[2];
+  __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kUmmaStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_tmem_full[a]), 1);
+      mbar_init(smem_u32(&bar_tmem_empty[a]), 128);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  // ---- tile walk (identical in every role) ---------------------------------------------------
+  const int NT = (p.N + BN - 1) / BN;
+  int total;
+  int MT = 0;
+  if constexpr (MODE == kWgrad) {
+    MT = (p.M + kUmmaBM - 1) / kUmmaBM;
+    total = p.E * MT * NT;
+  } else {
+    total = p.header[kHdrRowTiles] * NT;
+  }
+  auto decode = [&](int id, int& e, int& row0, int& n0, int& kb_begin_row, int& kblocks) {
+    if constexpr (MODE == kWgrad) {
+      e = id / (MT * NT);
+      const int rem = id - e * (MT * NT);
+      const int nt = rem / MT;
+      row0 = (rem - nt * MT) * kUmmaBM;
+      n0 = nt * BN;
+      kb_begin_row = p.pad_off[e];
+      kblocks = (p.pad_off[e + 1] - kb_begin_row) / kUmmaBK;
+    } else {
+      const int u = id / NT;
+      e = p.tile_expert[u];
+      const int first = p.pad_off[e] / kTileM;
+      const int cnt = (p.pad_off[e + 1] - p.pad_off[e]) / kTileM;
+      const int local = id - first * NT;
+      const int nt = local / cnt;
+      row0 = (first + (local - nt * cnt)) * kUmmaBM;
+      n0 = nt * BN;
+      kb_begin_row = 0;
+      kblocks = p.K / kUmmaBK;
+    }
+  };
+
+  if (warp == 0) {
+    // =========================== TMA producer ================================================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
+        int e, row0, n0, krow, kblocks;
+        decode(id, e, row0, n0, krow, kblocks);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
+            abort_flag = 1;
+            atomicMax(p.header + kHdrStatus, (int)kStatusProducerTimeout);
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          const uint32_t sa = smem_base + stage * SM::kStageBytes;
+          const uint32_t sb = sa + SM::kABytes;
+          mbar_expect_tx(full, SM::kStageBytes);
+          if constexpr (MODE == kWgrad) {
+            const int r = krow + kb * kUmmaBK;
+#pragma unroll
+            for (int i = 0; i < kUmmaBM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, row0 + i * 64, r, full);
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmB, n0 + i * 64, r, full);
+          } else {
+            tma_load_2d(sa, &tmA, kb * kUmmaBK, row0, full);
+            if constexpr (MODE == kFwd) {
+#pragma unroll
+              for (int i = 0; i < BN / 64; ++i) tma_load_3d(sb + i * 8192, &tmB, n0 + i * 64, kb * kUmmaBK, e, full);
+            } else {
+              tma_load_3d(sb, &tmB, kb * kUmmaBK, n0, e, full);
+            }
+          }
+          if (++stage == kUmmaStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // =========================== MMA issuer ==================================================
+    if (lane == 0) {
+      constexpr bool kAMn = (MODE == kWgrad);
+      constexpr bool kBMn = (MODE != kDgrad);
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kAMn ? 1u : 0u) << 15) |
+                                 ((kBMn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                 ((uint32_t)(kUmmaBM >> 4) << 24);
+      constexpr uint32_t a_kstep = kAMn ? (16 * 128) >> 4 : 32 >> 4;   // descriptor units of 16 bytes
+      constexpr uint32_t b_kstep = kBMn ? (16 * 128) >> 4 : 32 >> 4;
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
+        int e, row0, n0, krow, kblocks;
+        decode(id, e, row0, n0, krow, kblocks);
+        if (kblocks == 0) continue;
+        if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
+          abort_flag = 1;
+          atomicMax(p.header + kHdrStatus, (int)kStatusMmaTimeout);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kUmmaAccStride;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
+            abort_flag = 1;
+            atomicMax(p.header + kHdrStatus, (int)kStatusMmaTimeout);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * SM::kStageBytes;
+          const uint32_t sb = sa + SM::kABytes;
+          const uint64_t adesc = kAMn ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
+          const uint64_t bdesc = kBMn ? make_smem_desc(sb, 8192, 1024) : make_smem_desc(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < kUmmaBK / 16; ++k)
+            tc_mma_bf16(d_tmem, adesc + (uint64_t)(k * a_kstep), bdesc + (uint64_t)(k * b_kstep), idesc,
+                        (uint32_t)((kb | k) != 0));
+          tc_commit(smem_u32(&bar_empty[stage]));
+          if (++stage == kUmmaStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&bar_tmem_full[acc]));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // =========================== epilogue (warps 2..5) =======================================
+    const int q = warp & 3;                    // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int id = blockIdx.x; id < total; id += gridDim.x) {
+      int e, row0, n0, krow, kblocks;
+      decode(id, e, row0, n0, krow, kblocks);
+      const int row = row0 + q * 32 + lane;
+      if (kblocks == 0) {
+        float z[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) z[i] = 0.f;
+        for (int c = 0; c < BN / 32; ++c)
+          if (n0 + c * 32 < p.N) epi.template apply<32>(e, row, n0 + c * 32, z);
+        continue;
+      }
+      if (!mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag)) {
+        abort_flag = 1;
+        atomicMax(p.header + kHdrStatus, (int)kStatusEpilogueTimeout);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + acc * kUmmaAccStride + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        if (n0 + c * 32 >= p.N) break;
+        float v[32];
+        tc_ld_32x32(t_row + c * 32, v);
+        epi.template apply<32>(e, row, n0 + c * 32, v);
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag != 0) {
+    // give copies that may still be in flight time to land before the shared memory is released
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: tensor maps and launch
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+inline bool umma_available() { return encode_tiled_fn() != nullptr; }
+
+// bf16 tensor map with 128-byte swizzle; dims / box innermost first, strides in bytes for dims 1...
+inline bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                     const uint32_t* box) {
+  cuuint64_t gd[3];
+  cuuint64_t gs[2];
+  cuuint32_t bx[3], es[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) gs[i] = strides[i];
+  CUresult r = encode_tiled_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gd,
+                                 gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+inline int umma_sm_count() {
+  static int n = []() {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+    return v;
+  }();
+  return n;
+}
+
+template <int MODE, class Epi>
+inline int launch_umma_gemm(const GemmArgs& g, const Epi& epi, int64_t max_rows, int64_t max_tiles,
+                            cudaStream_t stream) {
+  constexpr int BN = 192;
+  using SM = UmmaSmem<BN>;
+  if (!umma_available()) return YAMOE_ERR_UNSUPPORTED;
+  CUtensorMap tmA, tmB;
+  bool ok = true;
+  if (MODE == kWgrad) {
+    const uint64_t da[2] = {(uint64_t)g.M, (uint64_t)max_rows}, sa[1] = {(uint64_t)g.lda * 2};
+    const uint32_t ba[2] = {64, 64};
+    ok = ok && make_map(&tmA, g.A, 2, da, sa, ba);
+    const uint64_t db[2] = {(uint64_t)g.N, (uint64_t)max_rows}, sb[1] = {(uint64_t)g.ldb * 2};
+    ok = ok && make_map(&tmB, g.B, 2, db, sb, ba);
+  } else {
+    const uint64_t da[2] = {(uint64_t)g.K, (uint64_t)max_rows}, sa[1] = {(uint64_t)g.lda * 2};
+    const uint32_t ba[2] = {64, 128};
+    ok = ok && make_map(&tmA, g.A, 2, da, sa, ba);
+    if (MODE == kFwd) {
+      const uint64_t db[3] = {(uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.E};
+      const uint64_t sb[2] = {(uint64_t)g.ldb * 2, (uint64_t)g.b_expert_stride * 2};
+      const uint32_t bb[3] = {64, 64, 1};
+      ok = ok && make_map(&tmB, g.B, 3, db, sb, bb);
+    } else {
+      const uint64_t db[3] = {(uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.E};
+      const uint64_t sb[2] = {(uint64_t)g.ldb * 2, (uint64_t)g.b_expert_stride * 2};
+      const uint32_t bb[3] = {64, (uint32_t)BN, 1};
+      ok = ok && make_map(&tmB, g.B, 3, db, sb, bb);
+    }
+  }
+  if (!ok) return YAMOE_ERR_CUDA;
+  auto kern = umma_gemm_kernel<MODE, BN, Epi>;
+  static bool attr_done = false;   // per template instantiation
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal) != cudaSuccess)
+      return YAMOE_ERR_CUDA;
+    attr_done = true;
+  }
+  UmmaParams p{g.M, g.N, g.K, g.E, g.tile_expert, g.pad_off, const_cast<int32_t*>(g.header)};
+  const int NT = (int)ceil_div(g.N, BN);
+  int64_t total_max = MODE == kWgrad ? (int64_t)g.E * ceil_div(g.M, kUmmaBM) * NT : max_tiles * NT;
+  int grid = (int)std::min<int64_t>(total_max, umma_sm_count());
+  if (grid <= 0) return YAMOE_OK;
+  kern<<<grid, kUmmaThreads, SM::kTotal, stream>>>(tmA, tmB, p, epi);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+}  // namespace yb

@@ -270,6 +270,52 @@ static int backward_impl(const void* grad_out, int per_slot, const void* hidden,
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
+// Uniform layout for the batched-matmul sub-operator: expert e owns rows [e*C, (e+1)*C).
+__global__ void uniform_tables_kernel(RouteTables rt, int E, int C) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i <= E) rt.pad_off[i] = i * C;
+  if (i < E) rt.counts[i] = C;
+  if (i < E * (C / kTileM)) rt.tile_expert[i] = i / (C / kTileM);
+  if (i == 0) {
+    rt.header[kHdrRowTiles] = E * (C / kTileM);
+    rt.header[kHdrRowsUsed] = E * C;
+  }
+}
+
+template <typename T>
+static int batch_mm_impl(const void* x, const void* w, void* out, int E, int C, int M, int N, int K, int mode,
+                         void* ws, cudaStream_t st) {
+  Plan p;
+  Bump b(ws);
+  carve_tables(b, p, (int64_t)E * C, E, 1, false);
+  const int path = current_path();
+  YB_CUDA_OK(cudaMemsetAsync(p.rt.header, 0, 16 * sizeof(int32_t), st));
+  const int nt = E * (C / kTileM) + E + 1;
+  uniform_tables_kernel<<<(unsigned)ceil_div(nt, 256), 256, 0, st>>>(p.rt, E, C);
+  const int64_t rows = (int64_t)E * C;
+  const bool tc = sizeof(T) == 2 && umma_available() && path != YAMOE_PATH_SIMT;
+  int rc = YAMOE_OK;
+  if (mode == kWgrad) {
+    EpiStore<T> epi{reinterpret_cast<T*>(out), M, N};
+    GemmArgs g{x, M, w, N, 0, M, N, 0, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+    if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma_gemm<kWgrad>(g, epi, rows, rows / kTileM, st); }
+    else launch_simt_gemm<T, kWgrad>(g, epi, rows, st);
+  } else {
+    EpiStoreRows<T> epi{reinterpret_cast<T*>(out), N};
+    if (mode == kFwd) {
+      GemmArgs g{x, K, w, N, (int64_t)K * N, 0, N, K, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+      if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma_gemm<kFwd>(g, epi, rows, rows / kTileM, st); }
+      else launch_simt_gemm<T, kFwd>(g, epi, rows, st);
+    } else {
+      GemmArgs g{x, K, w, K, (int64_t)K * N, 0, N, K, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+      if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma_gemm<kDgrad>(g, epi, rows, rows / kTileM, st); }
+      else launch_simt_gemm<T, kDgrad>(g, epi, rows, st);
+    }
+  }
+  if (rc) return rc;
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
 }  // namespace yb
 
 using namespace yb;
@@ -396,6 +442,28 @@ int yamoe_b200_experts_backward(const void* grad_out, int grad_out_per_slot, con
                               routing_cols, gate_up_proj, gate_up_proj_bias, down_proj, down_proj_bias, d_hidden,
                               d_routing, d_gate_up_proj, d_gate_up_proj_bias, d_down_proj, d_down_proj_bias, T, H,
                               E, K, expert_capacity, dtype, workspace, st);
+}
+
+size_t yamoe_b200_batch_mm_workspace_bytes(int E, int C) {
+  if (E <= 0 || C <= 0) return 0;
+  Plan p;
+  Bump b(nullptr);
+  carve_tables(b, p, (int64_t)E * C, E, 1, false);
+  return b.off + 256;
+}
+
+int yamoe_b200_batch_mm(const void* x, const void* weights, void* out, int E, int C, int M, int N, int K,
+                        int mode, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
+  if (!x || !weights || !out || E <= 0 || C <= 0 || N <= 0 || mode < 0 || mode > 2) return YAMOE_ERR_BAD_ARG;
+  if (mode == kWgrad ? (M <= 0) : (K <= 0)) return YAMOE_ERR_BAD_ARG;
+  if (C % kTileM != 0 || N % 64 != 0 || (mode == kWgrad ? M % 64 != 0 : K % 64 != 0)) return YAMOE_ERR_UNSUPPORTED;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < yamoe_b200_batch_mm_workspace_bytes(E, C))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == YAMOE_BF16) return batch_mm_impl<__nv_bfloat16>(x, weights, out, E, C, M, N, K, mode, workspace, st);
+  return batch_mm_impl<float>(x, weights, out, E, C, M, N, K, mode, workspace, st);
 }
 
 int yamoe_b200_device_status(const void* workspace, void* stream, int32_t* status_out) {

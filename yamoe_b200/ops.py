@@ -22,6 +22,8 @@ torch.library.define(
     "Tensor gate_up_proj, Tensor gate_up_proj_bias, Tensor down_proj, Tensor down_proj_bias, "
     "int expert_capacity, int num_experts, int top_k) -> Tensor[]")
 torch.library.define("yamoe_b200::sort", "(Tensor x, int end_bit, Tensor(a!) x_out, Tensor(b!) iota_out) -> ()")
+torch.library.define("yamoe_b200::batch_mm",
+                     "(Tensor x, Tensor weights, Tensor batch_sizes, Tensor(a!) output, bool trans_b=False) -> Tensor")
 torch.library.define("yamoe_b200::bincount_cumsum", "(Tensor input, Tensor(a!) output, int minlength) -> ()")
 
 
@@ -164,7 +166,38 @@ def _bincount_cumsum_cuda(input, output, minlength):
     output[:minlength].copy_(bins[:minlength])
 
 
+def _batch_mm_raw(x, weights, out, mode):
+    E, C = x.shape[0], x.shape[1]
+    M = x.shape[2] if mode == 2 else 0
+    K = 0 if mode == 2 else x.shape[2]
+    N = out.shape[2]
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        ws = _workspace(L.yamoe_b200_batch_mm_workspace_bytes(E, C), x.device)
+        st = L.yamoe_b200_batch_mm(x.data_ptr(), weights.data_ptr(), out.data_ptr(), E, C, M, N, K, mode,
+                                   _DT[x.dtype], ws.data_ptr(), ws.numel(), _stream())
+        _lib.check(st, "batch_mm")
+    return out
+
+
+@torch.library.impl("yamoe_b200::batch_mm", "CUDA")
+def _batch_mm_cuda(x, weights, batch_sizes, output, trans_b=False):
+    """reference: csrc/batch_mm.cu:7-31.  x [E,C,K]; weights [E,K,N] or, with trans_b, [E,N,K];
+    output [E,C,N].  `batch_sizes` is accepted and ignored, as in the reference."""
+    _require(x.dim() == 3 and weights.dim() == 3 and output.dim() == 3, "batch_mm: 3D tensors expected")
+    _require(x.dtype in _DT and weights.dtype == x.dtype and output.dtype == x.dtype, "batch_mm: dtype mismatch")
+    _require(x.is_contiguous() and weights.is_contiguous() and output.is_contiguous(), "batch_mm: contiguous tensors expected")
+    return _batch_mm_raw(x, weights, output, 1 if trans_b else 0)
+
+
+def batch_mm_wgrad(x, y):
+    """out[e] = x[e]^T @ y[e] for x [E,C,M], y [E,C,N]: the weight-gradient arrangement."""
+    out = torch.empty(x.shape[0], x.shape[2], y.shape[2], dtype=x.dtype, device=x.device)
+    return _batch_mm_raw(x.contiguous(), y.contiguous(), out, 2)
+
+
 experts = torch.ops.yamoe_b200.experts
+batch_mm = torch.ops.yamoe_b200.batch_mm
 experts_backward = torch.ops.yamoe_b200.experts_backward
 sort = torch.ops.yamoe_b200.sort
 bincount_cumsum = torch.ops.yamoe_b200.bincount_cumsum
