@@ -1,0 +1,337 @@
+"""Benchmark of the expert forward path (and, by flag, its other workloads) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line.  A "step" is one call of `yamoe_b200.experts` on one batch of seeded
+synthetic input.  The default workload is the GPT-OSS-20B-shaped expert layer forward: 4096
+tokens, hidden 2880, 32 experts, top-4, bf16 (weights and biases N(0, 0.02), activations N(0, 1),
+softmax/top-4 routing without renormalisation).
+
+* `value`      tokens/s with all inputs resident in HBM, timed with CUDA events over K steps,
+               barrier + synchronize on both sides, max over ranks.
+* `e2e`        the same metric through the public op with HOST inputs: every step copies the step's
+               inputs (hidden_states, router_indices, routing_weights) from pinned host memory to
+               the device and reads the [T, H] result back, inside the timed region.  Expert
+               weights are model state and stay resident.
+* `roofline`   gate_up grouped GEMM (the dominant kernel): algorithmic 4*S*H^2 FLOP per launch
+               divided by its mean device time, bracketed by CUDA events inside each timed step.
+* `cpu_baseline`  the CPU port of the reference's PyTorch implementation, timed on this box's host
+               cores on a bounded sample (rank 0, N=1 only).
+* `--impl reference`  times that CPU implementation with all host threads on the same workload.
+
+With N > 1 (torchrun) every rank runs the same workload on its own tokens with a full replica of
+the experts: tokens are independent units, so there is no data-path collective (weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+KEYS = ["hidden_states", "router_indices", "routing_weights", "gate_up_proj", "gate_up_proj_bias",
+        "down_proj", "down_proj_bias"]
+
+WORKLOADS = {
+    # name: (T, H, E, K, mode)
+    "gptoss20b_fwd_t4096": dict(T=4096, H=2880, E=32, K=4, mode="fwd"),
+    "gptoss20b_bwd_t8192": dict(T=8192, H=2880, E=32, K=4, mode="bwd"),
+    "gptoss120b_decode_t1": dict(T=1, H=2880, E=128, K=4, mode="fwd"),
+    "gptoss120b_decode_t4": dict(T=4, H=2880, E=128, K=4, mode="fwd"),
+    "gptoss120b_decode_t16": dict(T=16, H=2880, E=128, K=4, mode="fwd"),
+    "gptoss120b_decode_t64": dict(T=64, H=2880, E=128, K=4, mode="fwd"),
+    "gptoss120b_prefill_t16384": dict(T=16384, H=2880, E=128, K=4, mode="fwd", skew=True),
+    "readme_fp32_t512": dict(T=512, H=2880, E=8, K=2, mode="fwd", fp32=True),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(bf16_tflops=d["bf16_tflops"], hbm_gbs=d["hbm_gbs"], source="measured")
+    return dict(bf16_tflops=1590.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+def make_workload(name):
+    import torch
+    from oracle import experts_oracle as orc  # seeded synthetic inputs only; never on the timed GPU path
+    w = WORKLOADS[name]
+    dtype = torch.float32 if w.get("fp32") else torch.bfloat16
+    if name == "readme_fp32_t512":
+        inp = orc.make_readme_inputs(batch=2)
+    else:
+        inp = orc.make_inputs(w["T"], w["H"], w["E"], w["K"], seed=42, dtype=dtype, skew=w.get("skew", False),
+                              with_grad=(w["mode"] == "bwd"))
+    return w, inp, dtype
+
+
+def cpu_reference_time(w, inp, dtype, budget_s=20.0, threads=None):
+    """Times the CPU port of the reference forward (sparse per-expert loop) in the workload's
+    dtype.  Returns (tokens_per_s, cores, sample description)."""
+    import torch
+    from oracle import experts_oracle as orc
+    if threads:
+        torch.set_num_threads(threads)
+    cores = torch.get_num_threads()
+    T, E, K = w["T"], w["E"], w["K"]
+    args = [inp[k] for k in KEYS]
+    cap = 256 if w.get("fp32") else T
+
+    def run():
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            if w["mode"] == "bwd":
+                orc.experts_backward_oracle(inp["grad_out"], *args, cap, E, K, compute_dtype=dtype)
+            else:
+                orc.experts_forward_oracle(*args, cap, E, K, compute_dtype=dtype)
+        return time.perf_counter() - t0
+
+    first = run()                               # warm-up, also sizes the sample
+    reps = max(1, min(3, int(budget_s / max(first, 1e-3)) - 1))
+    best = min([run() for _ in range(reps)] + ([first] if reps == 1 and first > budget_s / 2 else []))
+    return T / best, cores, f"full workload ({T} tokens), best of {reps} after 1 warm-up, {dtype}, {cores} threads"
+
+
+def run_reference(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w, inp, dtype = make_workload(args.workload)
+    torch.set_num_threads(os.cpu_count() or 1)
+    T = w["T"]
+    args_list = [inp[k] for k in KEYS]
+    from oracle import experts_oracle as orc
+    cap = 256 if w.get("fp32") else T
+
+    def step():
+        with torch.no_grad():
+            if w["mode"] == "bwd":
+                orc.experts_backward_oracle(inp["grad_out"], *args_list, cap, w["E"], w["K"], compute_dtype=dtype)
+            else:
+                orc.experts_forward_oracle(*args_list, cap, w["E"], w["K"], compute_dtype=dtype)
+
+    steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
+    for _ in range(warm):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    cores = torch.get_num_threads()
+    val = T / dt
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
+        "data": "synthetic (seeded, shapes of the reference's own benchmarks)",
+        "config": {"workload": args.workload, "tokens": T, "hidden": w["H"], "experts": w["E"], "top_k": w["K"],
+                   "pass": w["mode"]},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"full workload ({T} tokens) per step, {steps} steps, CPU port of the "
+                                   f"reference's PyTorch experts (sparse branch), {cores} threads"},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import yamoe_b200
+    from yamoe_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; yamoe_b200 has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    w, inp, dtype = make_workload(args.workload)
+    T, H, E, K = w["T"], w["H"], w["E"], w["K"]
+    cap = 256 if w.get("fp32") else T
+    dev = [inp[k].cuda() for k in KEYS]
+    grad_out = inp["grad_out"].cuda() if w["mode"] == "bwd" else None
+    L = _lib.lib()
+
+    def step():
+        if w["mode"] == "bwd":
+            return yamoe_b200.experts_backward(grad_out, *dev, cap, E, K)
+        return yamoe_b200.experts(*dev, cap, E, K)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+
+    # ---- device-resident timing, with the gate_up GEMM bracketed by its own events ------------
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in pairs:
+        a.record(); b.record()           # forces creation of the underlying cudaEvent_t
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    t_start.record()
+    for a, b in pairs:
+        L.yamoe_b200_set_stage_events(a.cuda_event, b.cuda_event, 1)
+        step()
+    t_stop.record()
+    sync_all()
+    L.yamoe_b200_set_stage_events(None, None, 0)
+    ms_total = t_start.elapsed_time(t_stop)
+    gemm_ms = [a.elapsed_time(b) for a, b in pairs] if w["mode"] == "fwd" else []
+    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    value = world * T / (ms_step * 1e-3)
+
+    # ---- end to end: host inputs in, host result out, every step -------------------------------
+    host_in = [inp[k].pin_memory() for k in KEYS[:3]]
+    host_out = torch.empty(T, H, dtype=dtype).pin_memory()
+    host_go = inp["grad_out"].pin_memory() if w["mode"] == "bwd" else None
+    h2d = sum(x.numel() * x.element_size() for x in host_in) + (host_go.numel() * host_go.element_size() if host_go is not None else 0)
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        a = [x.to("cuda", non_blocking=True) for x in host_in]
+        if w["mode"] == "bwd":
+            g = host_go.to("cuda", non_blocking=True)
+            outs = yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K)
+            host_out.copy_(outs[0], non_blocking=True)
+        else:
+            out = yamoe_b200.experts(*a, *dev[3:], cap, E, K)
+            host_out.copy_(out, non_blocking=True)
+
+    for _ in range(min(args.warmup, 3)):
+        e2e_step()
+    sync_all()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e_stop.record()
+    sync_all()
+    clocks = sampler.stop()
+    te = torch.tensor([e_start.elapsed_time(e_stop)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_value = world * T / (te.item() / args.steps * 1e-3)
+
+    if rank == 0:
+        peaks = measured_peaks()
+        S = T * K
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
+            "data": "synthetic (seeded, shapes of the reference's own benchmarks)",
+            "config": {"workload": args.workload, "tokens": T, "hidden": H, "experts": E, "top_k": K,
+                       "pass": w["mode"], "expert_capacity": cap,
+                       "parallelism": f"dp{world} (token shards, replicated experts, no collective)",
+                       "l2": "expert weights (1.6 GB) exceed the 126 MB L2; no flush between steps"},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * (6 if w["mode"] == "fwd" else 14),
+            "clocks": clocks,
+            "achieved_tflops_whole_op": (6 if w["mode"] == "fwd" else 16) * S * H * H / (ms_step * 1e-3) / 1e12,
+        }
+        if gemm_ms:
+            mean_ms = sum(gemm_ms) / len(gemm_ms)
+            achieved = 4.0 * S * H * H / (mean_ms * 1e-3) / 1e12
+            line["roofline"] = {"bound": "tensor", "kernel": "umma_gemm_kernel<gate_up + bias + clamped SwiGLU>",
+                                "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                "frac": achieved / peaks["bf16_tflops"], "traffic": args.traffic,
+                                "kernel_ms": mean_ms, "peak_source": peaks["source"] + " (burst bf16 matmul)",
+                                "frac_of_nominal_2250": achieved / 2250.0}
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, sample = cpu_reference_time(w, inp, dtype)
+            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gptoss20b_fwd_t4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--traffic", type=float, default=1.269e9,
+                    help="DRAM bytes per launch of the dominant kernel from an ncu capture (see profiles/)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

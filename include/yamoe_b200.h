@@ -52,6 +52,11 @@ const char *yamoe_b200_status_string(int status);
 /* Process-wide path override used by tests and the benchmark; returns the previous value. */
 int yamoe_b200_set_path(int path);
 
+/* Profiling aid, process-wide and not thread-safe: while `stage` is non-zero, every forward call
+ * records `start_event` / `stop_event` (cudaEvent_t) on its stream immediately before / after
+ * the kernels of that stage: 1 gate_up GEMM, 2 down GEMM, 3 routing, 4 row gather; 0 disables. */
+int yamoe_b200_set_stage_events(void *start_event, void *stop_event, int stage);
+
 /* ---------------------------------------------------------------------------------------------
  * Routing: stable sort of the S = T*K (token, slot) assignments by expert id, per-expert
  * histogram and inclusive prefix sum.  Replaces sort_cuda (csrc/sort.cu:61-91) and

@@ -20,6 +20,7 @@ SIGNATURES = {
     "yamoe_b200_version": (c_int, []),
     "yamoe_b200_status_string": (ctypes.c_char_p, [c_int]),
     "yamoe_b200_set_path": (c_int, [c_int]),
+    "yamoe_b200_set_stage_events": (c_int, [c_void_p, c_void_p, c_int]),
     "yamoe_b200_route_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "yamoe_b200_route": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_forward_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),

@@ -7,9 +7,9 @@
 //   kDgrad  A rows K-major (TMA 2D),           B = W[e][n][k]  K-major  (TMA 3D)
 //   kWgrad  A = act[r][m] MN-major (TMA 2D),   B = grad[r][n]  MN-major (TMA 2D), k = rows of e
 //
-// CTA = 6 warps: warp 0 issues TMA loads into a 5-stage shared-memory ring (128-byte swizzle),
-// warp 1 allocates TMEM and issues tcgen05.mma (128 x BN x 16 per instruction, one elected
-// thread), warps 2..5 drain the fp32 accumulator from TMEM with tcgen05.ld and run the epilogue
+// CTA = 6 warps: warp 0 issues TMA loads into a 4-stage shared-memory ring (128-byte swizzle,
+// 48 KB per stage at BN = 256), warp 1 allocates TMEM and issues tcgen05.mma (128 x BN x 16 per
+// instruction, one elected thread), warps 2..5 drain the fp32 accumulator from TMEM with tcgen05.ld and run the epilogue
 // functor.  Two accumulators (2 x 256 TMEM columns) let the epilogue of tile i overlap the
 // main loop of tile i+1.  Tiles are walked expert by expert with the row tile varying fastest,
 // so the CTAs running at any moment share one expert's weight slab in L2.
@@ -20,6 +20,8 @@
 #pragma once
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "epilogues.cuh"
 #include "simt_gemm.cuh"
@@ -28,7 +30,6 @@ namespace yb {
 
 constexpr int kUmmaBM = 128;
 constexpr int kUmmaBK = 64;            // 64 bf16 = one 128-byte swizzle row
-constexpr int kUmmaStages = 5;
 constexpr int kUmmaThreads = 192;
 constexpr int kUmmaAccStride = 256;    // TMEM columns between the two accumulators
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
@@ -140,7 +141,8 @@ struct UmmaSmem {
   static constexpr int kABytes = kUmmaBM * 128;
   static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kTotal = kUmmaStages * kStageBytes + 1024;   // + slack for 1024-byte alignment
+  static constexpr int kStages = (227 * 1024 - 2048) / kStageBytes;  // 7 / 5 / 4 stages for BN 128 / 192 / 256
+  static constexpr int kTotal = kStages * kStageBytes + 1024;       // + slack for 1024-byte alignment
 };
 
 template <int MODE, int BN, class Epi>
@@ -148,6 +150,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const UmmaParams p, const Epi epi) {
   using SM = UmmaSmem<BN>;
+  constexpr int kUmmaStages = SM::kStages;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kUmmaStages];
   __shared__ __align__(8) uint64_t bar_empty[kUmmaStages];
@@ -402,10 +405,19 @@ inline int umma_sm_count() {
   return n;
 }
 
-template <int MODE, class Epi>
-inline int launch_umma_gemm(const GemmArgs& g, const Epi& epi, int64_t max_rows, int64_t max_tiles,
-                            cudaStream_t stream) {
-  constexpr int BN = 192;
+// Output-tile width of the tcgen05 GEMMs (128, 192 or 256 columns); YAMOE_B200_BN overrides.
+inline int umma_tile_n() {
+  static int bn = []() {
+    const char* env = std::getenv("YAMOE_B200_BN");
+    int v = env ? std::atoi(env) : 0;
+    return (v == 128 || v == 192 || v == 256) ? v : 256;
+  }();
+  return bn;
+}
+
+template <int MODE, int BN, class Epi>
+inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_rows, int64_t max_tiles,
+                               cudaStream_t stream) {
   using SM = UmmaSmem<BN>;
   if (!umma_available()) return YAMOE_ERR_UNSUPPORTED;
   CUtensorMap tmA, tmB;
@@ -447,6 +459,16 @@ inline int launch_umma_gemm(const GemmArgs& g, const Epi& epi, int64_t max_rows,
   if (grid <= 0) return YAMOE_OK;
   kern<<<grid, kUmmaThreads, SM::kTotal, stream>>>(tmA, tmB, p, epi);
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+template <int MODE, class Epi>
+inline int launch_umma_gemm(const GemmArgs& g, const Epi& epi, int64_t max_rows, int64_t max_tiles,
+                            cudaStream_t stream) {
+  switch (umma_tile_n()) {
+    case 128: return launch_umma_gemm_bn<MODE, 128>(g, epi, max_rows, max_tiles, stream);
+    case 192: return launch_umma_gemm_bn<MODE, 192>(g, epi, max_rows, max_tiles, stream);
+    default: return launch_umma_gemm_bn<MODE, 256>(g, epi, max_rows, max_tiles, stream);
+  }
 }
 
 }  // namespace yb

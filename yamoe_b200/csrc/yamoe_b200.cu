@@ -33,6 +33,26 @@ static int current_path() {
   return p;
 }
 
+// Optional CUDA-event bracket around one stage of the forward / backward sequence, for
+// benchmarks that need the device time of a single kernel inside a full call.
+struct StageEvents {
+  std::atomic<int> stage{0};
+  std::atomic<void*> start{nullptr}, stop{nullptr};
+};
+static StageEvents g_events;
+enum Stage { kStageNone = 0, kStageGateUp = 1, kStageDown = 2, kStageRoute = 3, kStageGather = 4 };
+
+struct StageTimer {
+  bool on;
+  cudaStream_t st;
+  StageTimer(int stage, cudaStream_t s) : on(g_events.stage.load() == stage && g_events.start.load()), st(s) {
+    if (on) cudaEventRecord(reinterpret_cast<cudaEvent_t>(g_events.start.load()), st);
+  }
+  ~StageTimer() {
+    if (on) cudaEventRecord(reinterpret_cast<cudaEvent_t>(g_events.stop.load()), st);
+  }
+};
+
 // Bump allocator over the caller's workspace; with base == nullptr it only measures.
 struct Bump {
   char* base;
@@ -155,12 +175,18 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
 
   int rc = prepare_routing(p, st);
   if (rc) return rc;
-  rc = launch_route<T>(ridx, reinterpret_cast<const T*>(rw), rcols, Tn, E, K, cap, p.rt, st);
+  {
+    StageTimer tm(kStageRoute, st);
+    rc = launch_route<T>(ridx, reinterpret_cast<const T*>(rw), rcols, Tn, E, K, cap, p.rt, st);
+  }
   if (rc) return rc;
   const unsigned row_blocks = (unsigned)ceil_div(p.max_rows, kRowWarps);
-  gather_rows_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const T*>(hidden),
-                                                              reinterpret_cast<T*>(p.xs), p.rt.row_token,
-                                                              p.rt.header, H);
+  {
+    StageTimer tm(kStageGather, st);
+    gather_rows_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const T*>(hidden),
+                                                                reinterpret_cast<T*>(p.xs), p.rt.row_token,
+                                                                p.rt.header, H);
+  }
   EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), reinterpret_cast<T*>(p.act), nullptr, nullptr,
                 p.rt.row_token, p.rt.row_weight, H};
   EpiScatterAdd<T, true, true> comb{reinterpret_cast<const T*>(bd), acc, p.rt.row_token, p.rt.row_weight, H};
@@ -169,14 +195,26 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
   GemmArgs g2{p.act, H, wd, H, (int64_t)H * H, 0, H, H, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
   if (use_tcgen05(path, dtype, H)) {
     if constexpr (sizeof(T) == 2) {
-      rc = launch_umma_gemm<kFwd>(g1, glu, p.max_rows, p.max_tiles, st);
+      {
+        StageTimer tm(kStageGateUp, st);
+        rc = launch_umma_gemm<kFwd>(g1, glu, p.max_rows, p.max_tiles, st);
+      }
       if (rc) return rc;
-      rc = launch_umma_gemm<kFwd>(g2, comb, p.max_rows, p.max_tiles, st);
+      {
+        StageTimer tm(kStageDown, st);
+        rc = launch_umma_gemm<kFwd>(g2, comb, p.max_rows, p.max_tiles, st);
+      }
       if (rc) return rc;
     }
   } else {
-    launch_simt_gemm<T, kFwd>(g1, glu, p.max_rows, st);
-    launch_simt_gemm<T, kFwd>(g2, comb, p.max_rows, st);
+    {
+      StageTimer tm(kStageGateUp, st);
+      launch_simt_gemm<T, kFwd>(g1, glu, p.max_rows, st);
+    }
+    {
+      StageTimer tm(kStageDown, st);
+      launch_simt_gemm<T, kFwd>(g2, comb, p.max_rows, st);
+    }
   }
   if (p.acc32) {
     const int64_t nv = Tn * H / 4;
@@ -341,6 +379,16 @@ int yamoe_b200_set_path(int path) {
   int prev = current_path();
   if (path >= YAMOE_PATH_AUTO && path <= YAMOE_PATH_GEMV) g_path.store(path);
   return prev;
+}
+
+int yamoe_b200_set_stage_events(void* start_event, void* stop_event, int stage) {
+  if (stage < kStageNone || stage > kStageGather) return YAMOE_ERR_BAD_ARG;
+  if (stage != kStageNone && (!start_event || !stop_event)) return YAMOE_ERR_BAD_ARG;
+  g_events.stage.store(kStageNone);
+  g_events.start.store(start_event);
+  g_events.stop.store(stop_event);
+  g_events.stage.store(stage);
+  return YAMOE_OK;
 }
 
 size_t yamoe_b200_route_workspace_bytes(int64_t T, int E, int K) {
