@@ -29,7 +29,8 @@ typedef enum {
   YAMOE_ERR_DTYPE = -3,          /* dtype is not YAMOE_F32 or YAMOE_BF16                      */
   YAMOE_ERR_CUDA = -4,           /* a CUDA runtime / driver call failed (launch, tensor map)  */
   YAMOE_ERR_UNSUPPORTED = -5,    /* valid request this build cannot serve                     */
-  YAMOE_ERR_DEVICE_TIMEOUT = -6  /* a bounded device-side wait gave up (see device status)    */
+  YAMOE_ERR_DEVICE_TIMEOUT = -6, /* a bounded device-side wait gave up (see device status)    */
+  YAMOE_ERR_STATIC_SCRATCH = -7  /* yamoe_b200_route_static: request exceeds its fixed scratch */
 } yamoe_status_t;
 
 typedef enum { YAMOE_F32 = 0, YAMOE_BF16 = 1 } yamoe_dtype_t;
@@ -73,6 +74,34 @@ size_t yamoe_b200_route_workspace_bytes(int64_t T, int E, int K);
 int yamoe_b200_route(const int64_t *router_indices, int32_t *sorted_values, int32_t *sorted_indices,
                      int32_t *bins, int32_t *counts, int64_t T, int E, int K,
                      void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Routing for callers that cannot hand over a workspace.  This entry point has no counterpart in
+ * the reference project.
+ *
+ * Same inputs, outputs and results as yamoe_b200_route, but it takes no workspace: the few
+ * hundred KB the routing kernels need besides their outputs (a ticket/status header, the padded
+ * offsets and the per-block histograms) live in a fixed 1 MiB array inside the library image.  It
+ * is meant for hosts that must not touch an allocator at the point of the call: a serving loop
+ * whose memory pool is frozen after start-up, a plugin interface that only passes input and output
+ * buffers, a runtime that forbids cudaMalloc on its worker threads.  The call itself performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ * Limits and rules:
+ *   - yamoe_b200_route_static_scratch_needed(T, E, K) must not exceed 1 MiB (1 048 576 bytes),
+ *     roughly ceil(T*K/2048) * E * 4 bytes; larger requests fail with YAMOE_ERR_STATIC_SCRATCH
+ *     and launch nothing.  E <= 1024 as everywhere else.
+ *   - The array exists once per GPU and costs 1 MiB of device memory on every GPU that loads the
+ *     library, until the process exits.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current) and caches it; make that first call outside of any stream capture.
+ *   - All calls on a device share the array and it keeps the previous call's contents; the part
+ *     that must start at zero is cleared on `stream` at the start of every call.  Two calls whose
+ *     GPU work can overlap (different streams without ordering) race on it: serialise them.
+ * ------------------------------------------------------------------------------------------- */
+size_t yamoe_b200_route_static_scratch_needed(int64_t T, int E, int K);
+int yamoe_b200_route_static(const int64_t *router_indices, int32_t *sorted_values, int32_t *sorted_indices,
+                            int32_t *bins, int32_t *counts, int64_t T, int E, int K, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Expert forward.  Replaces experts_cuda (csrc/moe.cpp:45-223; schema

@@ -23,6 +23,8 @@ SIGNATURES = {
     "yamoe_b200_set_stage_events": (c_int, [c_void_p, c_void_p, c_int]),
     "yamoe_b200_route_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "yamoe_b200_route": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_route_static_scratch_needed": (c_size_t, [c_int64, c_int, c_int]),
+    "yamoe_b200_route_static": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int, c_void_p]),
     "yamoe_b200_forward_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
     "yamoe_b200_experts_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 5 +
                                    [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),

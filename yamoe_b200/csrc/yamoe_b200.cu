@@ -6,6 +6,7 @@
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 #include "epilogues.cuh"
@@ -354,6 +355,41 @@ static int batch_mm_impl(const void* x, const void* w, void* out, int E, int C, 
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
+// ---- routing without a caller workspace -------------------------------------------------
+// Scratch for yamoe_b200_route_static.  It is part of the library image: every GPU that loads the
+// library keeps these bytes reserved until the process exits.  All calls on one device share it.
+constexpr size_t kStaticScratchBytes = 1u << 20;
+static __device__ __align__(256) unsigned char g_route_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxStaticDevices = 64;
+static void* g_static_scratch_addr[kMaxStaticDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+// Device address of the static scratch on the current device.  In host code the array's name
+// is only a handle, so the address is asked for once per device and remembered.
+static int static_scratch_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxStaticDevices) return YAMOE_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_route_static_scratch) != cudaSuccess || p == nullptr) return YAMOE_ERR_CUDA;
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return YAMOE_OK;
+}
+
+// Scratch the routing kernels need besides their outputs; with base == nullptr it only measures.
+static size_t carve_static_route(void* base, RouteTables& rt, int64_t S, int E) {
+  Bump b(base);
+  rt.header = b.take<int32_t>(16);
+  rt.counts = b.take<int32_t>(E);
+  rt.pad_off = b.take<int32_t>(E + 1);
+  rt.block_counts = b.take<int32_t>((size_t)route_blocks(S) * E);
+  return b.off;
+}
+
 }  // namespace yb
 
 using namespace yb;
@@ -371,6 +407,7 @@ const char* yamoe_b200_status_string(int s) {
     case YAMOE_ERR_CUDA: return "CUDA call failed";
     case YAMOE_ERR_UNSUPPORTED: return "unsupported configuration";
     case YAMOE_ERR_DEVICE_TIMEOUT: return "bounded device-side wait gave up";
+    case YAMOE_ERR_STATIC_SCRATCH: return "request needs more than the 1 MiB static scratch of yamoe_b200_route_static";
     default: return "unknown status";
   }
 }
@@ -424,6 +461,41 @@ int yamoe_b200_route(const int64_t* router_indices, int32_t* sorted_values, int3
     return YAMOE_OK;
   }
   return launch_route<float>(router_indices, nullptr, E, T, E, K, (int64_t)1 << 40, p.rt, st);
+}
+
+size_t yamoe_b200_route_static_scratch_needed(int64_t T, int E, int K) {
+  if (T < 0 || E <= 0 || K <= 0) return 0;
+  RouteTables rt;
+  return carve_static_route(nullptr, rt, T * K, E);
+}
+
+int yamoe_b200_route_static(const int64_t* router_indices, int32_t* sorted_values, int32_t* sorted_indices,
+                            int32_t* bins, int32_t* counts, int64_t T, int E, int K, void* stream) {
+  int rc = check_common(T, 8, E, K, YAMOE_F32);
+  if (rc) return rc;
+  if (!router_indices || !sorted_values || !sorted_indices || !bins) return YAMOE_ERR_BAD_ARG;
+  RouteTables rt{};
+  if (carve_static_route(nullptr, rt, T * K, E) > kStaticScratchBytes) return YAMOE_ERR_STATIC_SCRATCH;
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  carve_static_route(scratch, rt, T * K, E);
+  rt.sorted_values = sorted_values;
+  rt.sorted_indices = sorted_indices;
+  rt.bins = bins;
+  if (counts) rt.counts = counts;
+  rt.tile_expert = nullptr;
+  rt.row_token = rt.row_flat = nullptr;
+  rt.row_weight = nullptr;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // the ticket counter and status words must start at zero; the array keeps the last call's contents
+  YB_CUDA_OK(cudaMemsetAsync(rt.header, 0, 16 * sizeof(int32_t), st));
+  if (T == 0) {
+    YB_CUDA_OK(cudaMemsetAsync(bins, 0, (size_t)(E + 1) * sizeof(int32_t), st));
+    if (counts) YB_CUDA_OK(cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int32_t), st));
+    return YAMOE_OK;
+  }
+  return launch_route<float>(router_indices, nullptr, E, T, E, K, (int64_t)1 << 40, rt, st);
 }
 
 size_t yamoe_b200_forward_workspace_bytes(int64_t T, int H, int E, int K, int dtype) {
