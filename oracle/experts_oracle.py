@@ -157,65 +157,9 @@ def experts_backward_oracle(grad_out, hidden_states, router_indices, routing_wei
     return d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd
 
 
-# ----------------------------------------------------------------------------------------------
-# Seeded synthetic workloads (shapes and distributions of the reference's own benchmarks:
-# readme_example.py:14-45, perf_plot.py:29-39).  Shared by the tests and the benchmark.
-# ----------------------------------------------------------------------------------------------
-
-def make_routing(T, E, K, gen, expert_bias=None):
-    """softmax over E logits, top-K without renormalisation, dense scatter
-    (readme_example.py:27-36)."""
-    logits = torch.randn(T, E, generator=gen)
-    if expert_bias is not None:
-        logits = logits + expert_bias
-    probs = torch.softmax(logits, dim=-1)
-    weights, indices = torch.topk(probs, K, dim=-1)
-    dense = torch.zeros(T, E)
-    dense.scatter_(1, indices, weights)
-    return indices.contiguous(), dense
-
-
-def make_inputs(T, H, E, K, seed=42, weight_std=0.02, bias_std=0.02, dtype=torch.float32,
-                skew=False, with_grad=False):
-    """Generation order: logits, hidden, gate_up, gate_up_bias, down, down_bias, (grad_out)."""
-    gen = torch.Generator().manual_seed(seed)
-    bias = None
-    if skew:
-        bias = -1.2 * torch.log(torch.arange(E, dtype=torch.float32) + 1.0)
-    indices, dense = make_routing(T, E, K, gen, bias)
-    hidden = torch.randn(T, H, generator=gen)
-    wgu = torch.randn(E, H, 2 * H, generator=gen) * weight_std
-    bgu = torch.randn(E, 2 * H, generator=gen) * bias_std
-    wd = torch.randn(E, H, H, generator=gen) * weight_std
-    bd = torch.randn(E, H, generator=gen) * bias_std
-    out = dict(hidden_states=hidden.to(dtype), router_indices=indices,
-               routing_weights=dense.to(dtype), gate_up_proj=wgu.to(dtype),
-               gate_up_proj_bias=bgu.to(dtype), down_proj=wd.to(dtype),
-               down_proj_bias=bd.to(dtype))
-    if with_grad:
-        out["grad_out"] = torch.randn(T, H, generator=gen).to(dtype)
-    return out
-
-
-def make_readme_inputs(batch=2, seq=256, H=2880, E=8, K=2, seed=42):
-    """The README workload (readme_example.py:15-45) at a chosen batch size: N(0,1)
-    weights, zero biases, fp32."""
-    torch.manual_seed(seed)
-    logits = torch.randn(batch, seq, E)
-    probs = torch.softmax(logits, dim=-1)
-    weights, indices = torch.topk(probs, K, dim=-1)
-    T = batch * seq
-    dense = torch.zeros(T, E, dtype=weights.dtype)
-    fi, fw = indices.reshape(-1, K), weights.reshape(-1, K)
-    dense[torch.arange(T).unsqueeze(1).expand(-1, K), fi] = fw
-    hidden = torch.randn(batch, seq, H)
-    wgu = torch.randn(E, H, 2 * H)
-    bgu = torch.zeros(E, 2 * H)
-    wd = torch.randn(E, H, H)
-    bd = torch.zeros(E, H)
-    return dict(hidden_states=hidden.view(T, H), router_indices=fi.contiguous(),
-                routing_weights=dense, gate_up_proj=wgu, gate_up_proj_bias=bgu,
-                down_proj=wd, down_proj_bias=bd)
+# Seeded synthetic workloads live in the package (they are inputs, not a checker) and are
+# re-exported here for the tests.
+from yamoe_b200.workloads import make_inputs, make_readme_inputs, make_routing  # noqa: E402,F401
 
 
 def check_close(x, ref, rtol, name="", rel_l2=None):

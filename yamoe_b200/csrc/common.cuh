@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/yamoe_b200.h"
 
 namespace yb {
@@ -62,5 +64,25 @@ struct RouteTables {
 };
 
 enum HeaderSlot { kHdrTicket = 0, kHdrRowTiles = 1, kHdrRowsUsed = 2, kHdrDropped = 3, kHdrStatus = 4 };
+
+// Optional CUDA-event bracket around one stage of the forward / backward sequence, for
+// benchmarks that need the device time of a single kernel inside a full call.
+struct StageEvents {
+  std::atomic<int> stage{0};
+  std::atomic<void*> start{nullptr}, stop{nullptr};
+};
+inline StageEvents g_events;
+enum Stage { kStageNone = 0, kStageGateUp = 1, kStageDown = 2, kStageRoute = 3, kStageGather = 4 };
+
+struct StageTimer {
+  bool on;
+  cudaStream_t st;
+  StageTimer(int stage, cudaStream_t s) : on(g_events.stage.load() == stage && g_events.start.load()), st(s) {
+    if (on) cudaEventRecord(reinterpret_cast<cudaEvent_t>(g_events.start.load()), st);
+  }
+  ~StageTimer() {
+    if (on) cudaEventRecord(reinterpret_cast<cudaEvent_t>(g_events.stop.load()), st);
+  }
+};
 
 }  // namespace yb

@@ -34,26 +34,6 @@ static int current_path() {
   return p;
 }
 
-// Optional CUDA-event bracket around one stage of the forward / backward sequence, for
-// benchmarks that need the device time of a single kernel inside a full call.
-struct StageEvents {
-  std::atomic<int> stage{0};
-  std::atomic<void*> start{nullptr}, stop{nullptr};
-};
-static StageEvents g_events;
-enum Stage { kStageNone = 0, kStageGateUp = 1, kStageDown = 2, kStageRoute = 3, kStageGather = 4 };
-
-struct StageTimer {
-  bool on;
-  cudaStream_t st;
-  StageTimer(int stage, cudaStream_t s) : on(g_events.stage.load() == stage && g_events.start.load()), st(s) {
-    if (on) cudaEventRecord(reinterpret_cast<cudaEvent_t>(g_events.start.load()), st);
-  }
-  ~StageTimer() {
-    if (on) cudaEventRecord(reinterpret_cast<cudaEvent_t>(g_events.stop.load()), st);
-  }
-};
-
 // Bump allocator over the caller's workspace; with base == nullptr it only measures.
 struct Bump {
   char* base;
@@ -76,6 +56,7 @@ struct Plan {
   void* xs = nullptr;      // [max_rows, H]   gathered hidden rows
   void* act = nullptr;     // [max_rows, H]   GLU output
   float* acc32 = nullptr;  // [T, H]          fp32 combine target when the output is bf16
+  int32_t* slab_done = nullptr;  // [ceil(H/64)] completion counters of the decode path
   // backward
   void* gys = nullptr;     // [max_rows, H]   gathered grad_y rows
   void* pre = nullptr;     // [max_rows, 2H]  biased pre-activations
@@ -118,6 +99,7 @@ static Plan plan_forward(void* ws, int64_t T, int H, int E, int K, int dtype) {
   p.xs = b.take<char>((size_t)p.max_rows * H * p.esize);
   p.act = b.take<char>((size_t)p.max_rows * H * p.esize);
   if (dtype == YAMOE_BF16) p.acc32 = b.take<float>((size_t)T * H);
+  p.slab_done = b.take<int32_t>((size_t)ceil_div(H, 64));
   p.bytes = b.off + 256;
   return p;
 }
@@ -166,13 +148,14 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
   Plan p = plan_forward(ws, Tn, H, E, K, dtype);
   const int path = current_path();
   float* acc = p.acc32 ? p.acc32 : reinterpret_cast<float*>(out);
-  YB_CUDA_OK(cudaMemsetAsync(acc, 0, (size_t)Tn * H * sizeof(float), st));
   if (Tn == 0) return YAMOE_OK;
 
   if (dtype == YAMOE_BF16 && (path == YAMOE_PATH_GEMV || (path == YAMOE_PATH_AUTO && gemv_preferred(Tn, E, K)))) {
-    int rc = launch_gemv_forward(hidden, ridx, rw, rcols, wgu, bgu, wd, bd, out, Tn, H, E, K, cap, p.act, acc, st);
+    int rc = launch_gemv_forward(hidden, ridx, rw, rcols, wgu, bgu, wd, bd, out, Tn, H, E, K, cap, p.act, acc,
+                                 p.slab_done, st);
     if (rc != YAMOE_ERR_UNSUPPORTED) return rc;
   }
+  YB_CUDA_OK(cudaMemsetAsync(acc, 0, (size_t)Tn * H * sizeof(float), st));
 
   int rc = prepare_routing(p, st);
   if (rc) return rc;
