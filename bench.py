@@ -47,7 +47,9 @@ WORKLOADS = {
     "gptoss120b_decode_t4": dict(T=4, H=2880, E=128, K=4, mode="fwd"),
     "gptoss120b_decode_t16": dict(T=16, H=2880, E=128, K=4, mode="fwd"),
     "gptoss120b_decode_t64": dict(T=64, H=2880, E=128, K=4, mode="fwd"),
-    "gptoss120b_prefill_t16384": dict(T=16384, H=2880, E=128, K=4, mode="fwd", skew=True),
+    # expert-parallel when launched on N > 1 GPUs: tokens sharded by rows, experts contiguously
+    "gptoss120b_prefill_t16384": dict(T=16384, H=2880, E=128, K=4, mode="fwd", skew=True, ep=True),
+    "gptoss20b_fwd_t8192_ep": dict(T=8192, H=2880, E=32, K=4, mode="fwd", ep=True),
     "readme_fp32_t512": dict(T=512, H=2880, E=8, K=2, mode="fwd", fp32=True),
 }
 
@@ -217,8 +219,21 @@ def run_ours(args):
     flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda") if decode else None
     grad_out = inp["grad_out"].cuda() if w["mode"] == "bwd" else None
     L = _lib.lib()
+    use_ep = bool(w.get("ep")) and world > 1
+    if use_ep:
+        from yamoe_b200 import ep
+        T_total = T
+        lo, hi = rank * (T // world), (rank + 1) * (T // world)
+        local_w = ep.shard_expert_weights(*dev[3:], rank, world)
+        inp = {k: (v[lo:hi] if k in KEYS[:3] else v) for k, v in inp.items()}
+        dev = [dev[i][lo:hi].contiguous() for i in range(3)] + list(local_w)
+        torch.cuda.empty_cache()
+        T = hi - lo
+        ep_stats = {}
 
     def step():
+        if use_ep:
+            return ep.ep_experts(*dev, cap, E, K, stats=ep_stats)
         if w["mode"] == "bwd":
             return yamoe_b200.experts_backward(grad_out, *dev, cap, E, K)
         return yamoe_b200.experts(*dev, cap, E, K)
@@ -283,6 +298,9 @@ def run_ours(args):
             g = host_go.to("cuda", non_blocking=True)
             outs = yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K)
             host_out.copy_(outs[0], non_blocking=True)
+        elif use_ep:
+            out = ep.ep_experts(*a, *dev[3:], cap, E, K)
+            host_out.copy_(out, non_blocking=True)
         else:
             out = yamoe_b200.experts(*a, *dev[3:], cap, E, K)
             host_out.copy_(out, non_blocking=True)
@@ -304,15 +322,19 @@ def run_ours(args):
 
     if rank == 0:
         peaks = measured_peaks()
-        S = T * K
+        S = ep_stats["rows_received"] if use_ep else T * K      # rows this rank's GEMMs process
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
+            "scaling": "strong" if use_ep else "weak", "vs_baseline": None,
+            "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
             "data": "synthetic (seeded, shapes of the reference's own benchmarks)",
             "config": {"workload": args.workload, "tokens": T, "hidden": H, "experts": E, "top_k": K,
                        "pass": w["mode"], "expert_capacity": cap,
-                       "parallelism": f"dp{world} (token shards, replicated experts, no collective)",
+                       "parallelism": (f"ep{world} (tokens sharded by rows, experts sharded contiguously, NCCL all-to-all "
+                                       f"dispatch + combine; rank-0 rows sent/received {ep_stats.get('rows_sent')}/"
+                                       f"{ep_stats.get('rows_received')})") if use_ep else
+                                      f"dp{world} (token shards, replicated experts, no collective)",
                        "l2": ("L2 flushed (256 MB write) between steps, each step timed by its own events" if decode
                               else f"expert weights ({weight_bytes / 1e9:.1f} GB) exceed the 126 MB L2; no flush")},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

@@ -165,6 +165,23 @@ size_t yamoe_b200_batch_mm_workspace_bytes(int E, int C);
 int yamoe_b200_batch_mm(const void *x, const void *weights, void *out, int E, int C, int M, int N, int K,
                         int mode, int dtype, void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Expert-parallel helpers (no counterpart in the reference, which is single-GPU).  Around an
+ * all-to-all exchange of rows between the ranks that own tokens and the ranks that own experts:
+ *   permute_rows   dst[j,:] = src[sorted_indices[j] / K, :]          rows in expert-sorted order
+ *   combine_rows   out[t,:] = sum_k w[t,k] * rows[pos(t*K+k), :]      pos = inverse of sorted_indices
+ * `sorted_indices` is the output of yamoe_b200_route (n_sorted entries; assignments missing from
+ * it contribute nothing).  combine_rows needs a workspace of T*K*4 bytes and accumulates in fp32
+ * in slot order, so it is deterministic.  The weights come from routing_weights[t, expert] when
+ * routing_cols == E and from routing_weights[t, k] when routing_cols == K, as in the forward op.
+ * ------------------------------------------------------------------------------------------- */
+int yamoe_b200_permute_rows(const void *src, const int32_t *sorted_indices, void *dst, int64_t S, int H, int K,
+                            int dtype, void *stream);
+int yamoe_b200_combine_rows(const void *rows, const int32_t *sorted_indices, int64_t n_sorted,
+                            const int64_t *router_indices, const void *routing_weights, int routing_cols,
+                            void *out, int64_t T, int H, int E, int K, int dtype, void *workspace,
+                            size_t workspace_bytes, void *stream);
+
 /* Device status word of the last forward/backward call that used `workspace`: 0 when every
  * bounded device-side wait completed, otherwise a code naming the wait that gave up.  Reads
  * 4 bytes from the device with cudaMemcpyAsync on `stream` and synchronises that stream. */

@@ -34,6 +34,9 @@ SIGNATURES = {
                                     [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_batch_mm_workspace_bytes": (c_size_t, [c_int, c_int]),
     "yamoe_b200_batch_mm": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_permute_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "yamoe_b200_combine_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64,
+                                        c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_device_status": (c_int, [c_void_p, c_void_p, ctypes.POINTER(ctypes.c_int32)]),
 }
 

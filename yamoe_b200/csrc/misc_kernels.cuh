@@ -132,4 +132,57 @@ __global__ void routing_grad_kernel(const float* __restrict__ gw_row, const int3
   DT<T>::st(d_routing + idx, gw_row[row]);
 }
 
+// ---- expert-parallel helpers ---------------------------------------------------------------
+// dst[j, :] = src[sorted_indices[j] / K, :]: rows in expert-sorted order, ready to be sent to
+// the ranks that own the experts.  One warp per row, 16-byte accesses.
+template <typename T>
+__global__ void __launch_bounds__(kRowWarps * 32)
+permute_rows_kernel(const T* __restrict__ src, const int32_t* __restrict__ sorted_indices, T* __restrict__ dst,
+                    int64_t S, int H, int K) {
+  const int64_t row = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+  if (row >= S) return;
+  const int lane = threadIdx.x & 31;
+  const int tok = sorted_indices[row] / K;
+  const int nvec = H * (int)sizeof(T) / 16;
+  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)tok * H);
+  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)row * H);
+  for (int i = lane; i < nvec; i += 32) d[i] = __ldg(s + i);
+}
+
+// inv[sorted_indices[j]] = j
+__global__ void invert_perm_kernel(const int32_t* __restrict__ sorted_indices, int32_t* __restrict__ inv, int64_t S) {
+  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j < S) inv[sorted_indices[j]] = (int32_t)j;
+}
+
+// out[t, :] = sum_k w[t, k] * rows[inv[t*K + k], :]   (fp32 accumulation, fixed order, one rounding).
+// The weighted combine of csrc/scatter.cu:67-108 for rows that came back from the expert owners.
+template <typename T>
+__global__ void __launch_bounds__(kRowWarps * 32)
+combine_rows_kernel(const T* __restrict__ rows, const int32_t* __restrict__ inv,
+                    const int64_t* __restrict__ router_indices, const T* __restrict__ routing_weights,
+                    int routing_cols, T* __restrict__ out, int64_t Tn, int H, int E, int K) {
+  const int64_t t = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+  if (t >= Tn) return;
+  const int lane = threadIdx.x & 31;
+  constexpr int VE = 16 / (int)sizeof(T);
+  const int nvec = H / VE;
+  for (int i = lane; i < nvec; i += 32) {
+    float acc[VE];
+#pragma unroll
+    for (int j = 0; j < VE; ++j) acc[j] = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int32_t r = inv[t * K + k];
+      if (r < 0) continue;
+      const int col = (routing_cols == E) ? (int)router_indices[t * K + k] : k;
+      const float w = DT<T>::ld(routing_weights + (size_t)t * routing_cols + col);
+      float v[VE];
+      load_vec<T, VE>(rows + (size_t)r * H + (size_t)i * VE, v);
+#pragma unroll
+      for (int j = 0; j < VE; ++j) acc[j] = fmaf(w, v[j], acc[j]);
+    }
+    store_vec<T, VE>(out + (size_t)t * H + (size_t)i * VE, acc);
+  }
+}
+
 }  // namespace yb

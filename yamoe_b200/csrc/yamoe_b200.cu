@@ -569,6 +569,52 @@ int yamoe_b200_batch_mm(const void* x, const void* weights, void* out, int E, in
   return batch_mm_impl<float>(x, weights, out, E, C, M, N, K, mode, workspace, st);
 }
 
+int yamoe_b200_permute_rows(const void* src, const int32_t* sorted_indices, void* dst, int64_t S, int H, int K,
+                            int dtype, void* stream) {
+  if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
+  if (S < 0 || H <= 0 || H % 8 != 0 || K <= 0) return YAMOE_ERR_BAD_ARG;
+  if (S == 0) return YAMOE_OK;
+  if (!src || !sorted_indices || !dst) return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned blocks = (unsigned)ceil_div(S, kRowWarps);
+  if (dtype == YAMOE_BF16)
+    permute_rows_kernel<__nv_bfloat16><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(src), sorted_indices, reinterpret_cast<__nv_bfloat16*>(dst), S, H, K);
+  else
+    permute_rows_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const float*>(src),
+                                                                 sorted_indices, reinterpret_cast<float*>(dst), S, H, K);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+int yamoe_b200_combine_rows(const void* rows, const int32_t* sorted_indices, int64_t n_sorted,
+                            const int64_t* router_indices, const void* routing_weights, int routing_cols, void* out,
+                            int64_t T, int H, int E, int K, int dtype, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
+  if (T < 0 || H <= 0 || H % 8 != 0 || K <= 0 || E <= 0 || n_sorted < 0 || n_sorted > T * K) return YAMOE_ERR_BAD_ARG;
+  if (routing_cols != E && routing_cols != K) return YAMOE_ERR_BAD_ARG;
+  if (T == 0) return YAMOE_OK;
+  if (!rows || !sorted_indices || !router_indices || !routing_weights || !out) return YAMOE_ERR_BAD_ARG;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < (size_t)T * K * sizeof(int32_t))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int32_t* inv = reinterpret_cast<int32_t*>(workspace);
+  YB_CUDA_OK(cudaMemsetAsync(inv, 0xFF, (size_t)T * K * sizeof(int32_t), st));
+  if (n_sorted > 0)
+    invert_perm_kernel<<<(unsigned)ceil_div(n_sorted, 256), 256, 0, st>>>(sorted_indices, inv, n_sorted);
+  const unsigned blocks = (unsigned)ceil_div(T, kRowWarps);
+  if (dtype == YAMOE_BF16)
+    combine_rows_kernel<__nv_bfloat16><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(rows), inv, router_indices,
+        reinterpret_cast<const __nv_bfloat16*>(routing_weights), routing_cols, reinterpret_cast<__nv_bfloat16*>(out),
+        T, H, E, K);
+  else
+    combine_rows_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const float*>(rows), inv, router_indices, reinterpret_cast<const float*>(routing_weights),
+        routing_cols, reinterpret_cast<float*>(out), T, H, E, K);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
 int yamoe_b200_device_status(const void* workspace, void* stream, int32_t* status_out) {
   if (!workspace || !status_out) return YAMOE_ERR_BAD_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

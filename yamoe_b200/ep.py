@@ -1,0 +1,112 @@
+"""Expert-parallel forward: the experts of one layer sharded contiguously over the ranks of a
+process group, tokens sharded by rows (data-parallel), one all-to-all each way.
+
+The reference is single-GPU and has nothing like this; the result must equal the single-GPU op
+(`yamoe_b200.experts`, hence `reference.py`) on the concatenated tokens with all experts.
+
+Per call, on every rank r (G ranks, E experts, E/G local experts, T_r local tokens):
+
+1. route      stable sort of the local (token, slot) assignments by global expert id -> counts[E]
+2. counts     all_to_all of the [G, E/G] count matrix: every rank learns how many rows each peer
+              sends for each of its local experts
+3. dispatch   rows hidden[token] in expert-sorted order (permute_rows kernel), all_to_all with the
+              split sizes of step 2
+4. compute    the received rows are tokens of a local problem with top_k = 1: expert id = local
+              expert, weight 1; one call of the expert op on the local weight shard.  Rows arrive
+              source-major and the op's sort is stable, so the capacity keeps the first C
+              assignments of an expert in global token order, exactly like the single-GPU op.
+5. combine    all_to_all back, then out[t] = sum_k w[t,k] * row(t,k) (combine_rows kernel)
+
+The split sizes of steps 3 and 5 live on the host because `all_to_all_single` wants them there:
+one device-to-host copy of 2*G integers per call.
+
+`Backend` bundles the compute steps so that the exchange logic can be exercised on CPU ranks
+(gloo) with stand-in compute; the default backend is the CUDA library, and nothing else ships.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class Backend:
+    route: Callable        # (router_indices [T,K], E) -> sorted_values, sorted_indices, bins, counts
+    permute_rows: Callable  # (hidden [T,H], sorted_indices, K) -> rows [S,H]
+    experts: Callable      # the expert op
+    combine_rows: Callable  # (rows [S,H], sorted_indices, router_indices, routing_weights, E) -> [T,H]
+
+
+def cuda_backend() -> Backend:
+    from . import ops
+    return Backend(route=ops.route, permute_rows=ops.permute_rows, experts=ops.experts,
+                   combine_rows=ops.combine_rows)
+
+
+def expert_range(rank: int, world: int, num_experts: int):
+    """Contiguous shard of experts owned by `rank`."""
+    if num_experts % world != 0:
+        raise ValueError(f"num_experts ({num_experts}) must be divisible by the group size ({world})")
+    per = num_experts // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_expert_weights(gate_up_proj, gate_up_proj_bias, down_proj, down_proj_bias, rank, world):
+    """Slices the four [E, ...] tensors to this rank's contiguous expert shard."""
+    lo, hi = expert_range(rank, world, gate_up_proj.shape[0])
+    return (gate_up_proj[lo:hi].contiguous(), gate_up_proj_bias[lo:hi].contiguous(),
+            down_proj[lo:hi].contiguous(), down_proj_bias[lo:hi].contiguous())
+
+
+def exchange_plan(counts: torch.Tensor, world: int, group=None):
+    """counts: int32/int64 [E] local histogram.  Returns (recv_counts [G, E/G] on the device,
+    send_splits, recv_splits as Python lists)."""
+    E = counts.numel()
+    per = E // world
+    send_counts = counts.to(torch.int64).view(world, per).contiguous()
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    both = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()
+    return recv_counts, both[0].tolist(), both[1].tolist()
+
+
+def ep_experts(hidden_states, router_indices, routing_weights, gate_up_local, gate_up_bias_local, down_local,
+               down_bias_local, expert_capacity: int, num_experts: int, top_k: int, group=None,
+               backend: Optional[Backend] = None, stats: Optional[dict] = None):
+    """Expert-parallel `experts`.  `hidden_states` [T_r, H], `router_indices` [T_r, K] (global expert
+    ids) and `routing_weights` [T_r, E] or [T_r, K] are this rank's token shard; the four weight
+    tensors are this rank's expert shard ([E/G, ...]).  Returns this rank's [T_r, H] output."""
+    be = backend or cuda_backend()
+    world = dist.get_world_size(group)
+    E, K = int(num_experts), int(top_k)
+    per = E // world
+    if gate_up_local.shape[0] != per:
+        raise RuntimeError(f"expected {per} local experts, got {gate_up_local.shape[0]}")
+    H = hidden_states.shape[1]
+
+    _, sorted_indices, _, counts = be.route(router_indices, E)
+    recv_counts, send_splits, recv_splits = exchange_plan(counts, world, group)
+    n_send, n_recv = sum(send_splits), sum(recv_splits)
+    sorted_indices = sorted_indices[:n_send]
+
+    rows = be.permute_rows(hidden_states, sorted_indices, K)
+    recv = torch.empty(n_recv, H, dtype=rows.dtype, device=rows.device)
+    dist.all_to_all_single(recv, rows, recv_splits, send_splits, group=group)
+
+    # local problem: one "token" per received row, top_k = 1, weight 1
+    local_ids = torch.repeat_interleave(
+        torch.arange(per, device=recv.device).repeat(world), recv_counts.view(-1).to(recv.device),
+        output_size=n_recv).view(n_recv, 1)
+    ones = torch.ones(n_recv, 1, dtype=recv.dtype, device=recv.device)
+    y = be.experts(recv, local_ids, ones, gate_up_local, gate_up_bias_local, down_local, down_bias_local,
+                   int(expert_capacity), per, 1)
+
+    back = torch.empty(n_send, H, dtype=y.dtype, device=y.device)
+    dist.all_to_all_single(back, y, send_splits, recv_splits, group=group)
+    out = be.combine_rows(back, sorted_indices, router_indices, routing_weights, E)
+    if stats is not None:
+        stats.update(rows_sent=n_send, rows_received=n_recv, send_splits=send_splits, recv_splits=recv_splits)
+    return out

@@ -196,6 +196,36 @@ def batch_mm_wgrad(x, y):
     return _batch_mm_raw(x.contiguous(), y.contiguous(), out, 2)
 
 
+def permute_rows(src: torch.Tensor, sorted_indices: torch.Tensor, top_k: int) -> torch.Tensor:
+    """rows[j] = src[sorted_indices[j] // top_k]: token rows in expert-sorted order."""
+    _require(src.is_cuda and src.dim() == 2 and src.dtype in _DT, "permute_rows: 2D CUDA float32/bfloat16 expected")
+    src, si = src.contiguous(), sorted_indices.contiguous()
+    out = torch.empty(si.numel(), src.shape[1], dtype=src.dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        st = _lib.lib().yamoe_b200_permute_rows(src.data_ptr(), si.data_ptr(), out.data_ptr(), si.numel(),
+                                                src.shape[1], int(top_k), _DT[src.dtype], _stream())
+        _lib.check(st, "permute_rows")
+    return out
+
+
+def combine_rows(rows: torch.Tensor, sorted_indices: torch.Tensor, router_indices: torch.Tensor,
+                 routing_weights: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """out[t] = sum_k w[t,k] * rows[position of assignment (t,k) in sorted_indices]."""
+    T, K = router_indices.shape
+    H = rows.shape[1]
+    rows, si = rows.contiguous(), sorted_indices.contiguous()
+    ri, rw = router_indices.to(torch.int64).contiguous(), routing_weights.contiguous()
+    _require(rows.dtype in _DT and rw.dtype == rows.dtype, "combine_rows: dtype mismatch")
+    out = torch.empty(T, H, dtype=rows.dtype, device=rows.device)
+    with torch.cuda.device(rows.device):
+        ws = _workspace(T * K * 4, rows.device)
+        st = _lib.lib().yamoe_b200_combine_rows(rows.data_ptr(), si.data_ptr(), si.numel(), ri.data_ptr(),
+                                                rw.data_ptr(), rw.shape[1], out.data_ptr(), T, H, int(num_experts), K,
+                                                _DT[rows.dtype], ws.data_ptr(), ws.numel(), _stream())
+        _lib.check(st, "combine_rows")
+    return out
+
+
 experts = torch.ops.yamoe_b200.experts
 batch_mm = torch.ops.yamoe_b200.batch_mm
 experts_backward = torch.ops.yamoe_b200.experts_backward
