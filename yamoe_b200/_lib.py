@@ -8,7 +8,10 @@ from __future__ import annotations
 import ctypes
 import os
 
-from .build import LIB_PATH
+from .build import LIB_PATH as _DEFAULT_LIB
+
+# YAMOE_B200_LIB points at an alternative build of the same library (profiling experiments)
+LIB_PATH = os.environ.get("YAMOE_B200_LIB") or _DEFAULT_LIB
 
 c_void_p, c_int, c_int64, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
 

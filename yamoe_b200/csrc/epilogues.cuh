@@ -220,7 +220,7 @@ struct EpiGluBackward {
         const float pg = p[2 * i], pu = p[2 * i + 1];
         const float gc = fminf(pg, kLimit);
         const float uc = fminf(fmaxf(pu, -kLimit), kLimit);
-        const float s = 1.0f / (1.0f + __expf(-kAlpha * gc));
+        const float s = __fdividef(1.0f, 1.0f + __expf(-kAlpha * gc));
         const float gate_act = gc * s;
         dot += v[i] * (uc + 1.0f) * gate_act;
         const float gi = w * v[i];
@@ -248,6 +248,29 @@ struct EpiStore {
   __device__ __forceinline__ void apply(int e, int row, int n0, const float (&v)[NV]) const {
     if (row >= M) return;
     store_vec<T, NV>(C + ((size_t)e * M + row) * N + n0, v);
+  }
+};
+
+// ---- down-projection epilogue for the two-step combine: y[row] = w_row * (v + bias) ------------
+// reference: csrc/moe.cpp:187 and the per-row scaling of csrc/scatter.cu:98-106.  The K rows of a
+// token are summed afterwards by combine_padded_kernel; padding rows are never read and are skipped.
+template <typename T>
+struct EpiWeightedRows {
+  const T* bias;             // [E, N]
+  T* y;                      // [rows, N]
+  const int32_t* row_token;
+  const float* row_weight;
+  int N;
+
+  template <int NV>
+  __device__ __forceinline__ void apply(int e, int row, int n0, const float (&v)[NV]) const {
+    if (row_token[row] < 0) return;
+    float o[NV];
+    load_vec<T, NV>(bias + (size_t)e * N + n0, o);
+    const float w = row_weight[row];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) o[i] = w * (o[i] + v[i]);
+    store_vec<T, NV>(y + (size_t)row * N + n0, o);
   }
 };
 

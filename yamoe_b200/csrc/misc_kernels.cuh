@@ -132,6 +132,37 @@ __global__ void routing_grad_kernel(const float* __restrict__ gw_row, const int3
   DT<T>::st(d_routing + idx, gw_row[row]);
 }
 
+// out[t, :] = sum over the kept slots k of y[flat_row[t*K + k], :]   (rows already weighted).
+// Second half of the combine (reference: csrc/scatter.cu:67-108): fp32 accumulation in slot
+// order, one rounding, every output element written exactly once (no zero-fill, no atomics).
+template <typename T>
+__global__ void __launch_bounds__(kRowWarps * 32)
+combine_padded_kernel(const T* __restrict__ y, const int32_t* __restrict__ flat_row, T* __restrict__ out,
+                      int64_t Tn, int H, int K) {
+  const int64_t t = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+  if (t >= Tn) return;
+  const int lane = threadIdx.x & 31;
+  constexpr int VE = 16 / (int)sizeof(T);
+  const int nvec = H / VE;
+  int32_t r[8];
+  const int kk = K < 8 ? K : 8;
+  for (int k = 0; k < kk; ++k) r[k] = flat_row[t * K + k];
+  for (int i = lane; i < nvec; i += 32) {
+    float acc[VE];
+#pragma unroll
+    for (int j = 0; j < VE; ++j) acc[j] = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int32_t row = k < 8 ? r[k] : flat_row[t * K + k];
+      if (row < 0) continue;
+      float v[VE];
+      load_vec<T, VE>(y + (size_t)row * H + (size_t)i * VE, v);
+#pragma unroll
+      for (int j = 0; j < VE; ++j) acc[j] += v[j];
+    }
+    store_vec<T, VE>(out + (size_t)t * H + (size_t)i * VE, acc);
+  }
+}
+
 // ---- expert-parallel helpers ---------------------------------------------------------------
 // dst[j, :] = src[sorted_indices[j] / K, :]: rows in expert-sorted order, ready to be sent to
 // the ranks that own the experts.  One warp per row, 16-byte accesses.

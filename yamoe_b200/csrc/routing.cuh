@@ -30,6 +30,7 @@ route_count_kernel(const int64_t* __restrict__ router_indices, int S, int E, int
   extern __shared__ int32_t smem_i[];
   int32_t* hist = smem_i;            // [E]
   int32_t* poff = smem_i + E;        // [E+1]
+  int32_t* qoff = smem_i + 2 * E + 1;  // [E+1]
   __shared__ int is_last;
   const int tid = threadIdx.x;
   for (int e = tid; e < E; e += kRouteThreads) hist[e] = 0;
@@ -67,7 +68,7 @@ route_count_kernel(const int64_t* __restrict__ router_indices, int S, int E, int
   }
   __syncthreads();
   if (tid == 0) {
-    int cum = 0, rows = 0, dropped = 0;
+    int cum = 0, rows = 0, dropped = 0, pairs = 0;
     for (int e = 0; e < E; ++e) {
       int c = hist[e];
       cum += c;
@@ -76,9 +77,16 @@ route_count_kernel(const int64_t* __restrict__ router_indices, int S, int E, int
       dropped += c - kept;
       poff[e] = rows;
       rt.pad_off[e] = rows;
-      rows += (kept + kTileM - 1) / kTileM * kTileM;
+      qoff[e] = pairs;
+      if (rt.pair_off != nullptr) rt.pair_off[e] = pairs;
+      const int tiles = (kept + kTileM - 1) / kTileM;
+      rows += tiles * kTileM;
+      pairs += (tiles + 1) / 2;
     }
     poff[E] = rows;
+    qoff[E] = pairs;
+    if (rt.pair_off != nullptr) rt.pair_off[E] = pairs;
+    rt.header[kHdrPairs] = pairs;
     rt.bins[E] = 0;
     rt.pad_off[E] = rows;
     rt.header[kHdrRowTiles] = rows / kTileM;
@@ -90,6 +98,10 @@ route_count_kernel(const int64_t* __restrict__ router_indices, int S, int E, int
   if (rt.tile_expert != nullptr) {
     for (int e = tid; e < E; e += kRouteThreads)
       for (int t = poff[e] / kTileM; t < poff[e + 1] / kTileM; ++t) rt.tile_expert[t] = e;
+  }
+  if (rt.pair_expert != nullptr) {
+    for (int e = tid; e < E; e += kRouteThreads)
+      for (int t = qoff[e]; t < qoff[e + 1]; ++t) rt.pair_expert[t] = e;
   }
 }
 
@@ -150,6 +162,7 @@ route_place_kernel(const int64_t* __restrict__ router_indices, const T* __restri
         const int t = p / K;
         rt.row_token[r] = t;
         rt.row_flat[r] = p;
+        rt.flat_row[p] = r;
         const int col = (routing_cols == E) ? e : (p - t * K);
         rt.row_weight[r] = DT<T>::ld(routing_weights + (size_t)t * routing_cols + col);
       }
@@ -166,7 +179,7 @@ inline int launch_route(const int64_t* router_indices, const T* routing_weights,
                         cudaStream_t stream) {
   const int S = (int)(T_tokens * K);
   const int nblk = (int)ceil_div(S, kRouteItems);
-  size_t smem1 = (size_t)(2 * E + 1) * sizeof(int32_t);
+  size_t smem1 = (size_t)(3 * E + 2) * sizeof(int32_t);
   size_t smem2 = (size_t)kRouteWarps * E * sizeof(int32_t);
   route_count_kernel<<<nblk, kRouteThreads, smem1, stream>>>(router_indices, S, E, capacity, rt, nblk);
   route_place_kernel<T><<<nblk, kRouteThreads, smem2, stream>>>(router_indices, routing_weights,

@@ -27,6 +27,8 @@ struct GemmArgs {
   const int32_t* tile_expert;
   const int32_t* pad_off;
   const int32_t* header;
+  const int32_t* pair_expert = nullptr;   // tile-pair tables (256-row tcgen05 kernel only)
+  const int32_t* pair_off = nullptr;
 };
 
 constexpr int kSimtBM = 64, kSimtBN = 64, kSimtBK = 16, kSimtThreads = 256;

@@ -101,8 +101,9 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uin
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+// Issues the TMEM load of 32 columns for this thread's lane; the registers are valid only after
+// tc_ld_wait().
+__device__ __forceinline__ void tc_ld_32x32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -112,9 +113,16 @@ __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Waits for the outstanding TMEM loads.  The registers are passed through the statement so that
+// the compiler cannot schedule any use of them before the wait.
+__device__ __forceinline__ void tc_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :: "memory");
 }
 
 // Shared-memory matrix descriptor (tcgen05 format): start address, leading / stride byte
@@ -331,12 +339,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t t_row = tmem_base + acc * kUmmaAccStride + ((uint32_t)(q * 32) << 16);
+      // two register buffers: the TMEM load of chunk c+1 is in flight while chunk c is processed
+      const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
+      uint32_t ra[32], rb[32];
+      tc_ld_32x32_issue(t_row, ra);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        if (n0 + c * 32 >= p.N) break;
-        float v[32];
-        tc_ld_32x32(t_row + c * 32, v);
-        epi.template apply<32>(e, row, n0 + c * 32, v);
+      for (int c = 0; c < nchunks; c += 2) {
+        tc_ld_wait(ra);
+        if (c + 1 < nchunks) tc_ld_32x32_issue(t_row + (c + 1) * 32, rb);
+        {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
+          epi.template apply<32>(e, row, n0 + c * 32, v);
+        }
+        if (c + 1 < nchunks) {
+          tc_ld_wait(rb);
+          if (c + 2 < nchunks) tc_ld_32x32_issue(t_row + (c + 2) * 32, ra);
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rb[i]);
+          epi.template apply<32>(e, row, n0 + (c + 1) * 32, v);
+        }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&bar_tmem_empty[acc]));

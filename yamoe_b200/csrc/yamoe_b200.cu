@@ -55,6 +55,7 @@ struct Plan {
   // forward
   void* xs = nullptr;      // [max_rows, H]   gathered hidden rows
   void* act = nullptr;     // [max_rows, H]   GLU output
+  void* yrows = nullptr;   // [max_rows, H]   weighted down-projection rows (bf16 two-step combine)
   float* acc32 = nullptr;  // [T, H]          fp32 combine target when the output is bf16
   int32_t* slab_done = nullptr;  // [ceil(H/64)] completion counters of the decode path
   // backward
@@ -77,16 +78,20 @@ static void carve_tables(Bump& b, Plan& p, int64_t T, int E, int K, bool rows) {
   p.rt.pad_off = b.take<int32_t>(E + 1);
   p.rt.block_counts = b.take<int32_t>((size_t)route_blocks(p.S) * E);
   p.rt.tile_expert = b.take<int32_t>(p.max_tiles);
+  p.rt.pair_off = b.take<int32_t>(E + 1);
+  p.rt.pair_expert = b.take<int32_t>(p.max_tiles);
   p.rt.sorted_values = b.take<int32_t>(p.S);
   p.rt.sorted_indices = b.take<int32_t>(p.S);
   if (rows) {
-    // row_token and row_flat are adjacent so that one memset marks every row as padding
-    p.rt.row_token = b.take<int32_t>(2 * (size_t)p.max_rows);
+    // row_token, row_flat and flat_row are adjacent so that one memset marks every row as padding
+    // and every assignment as dropped
+    p.rt.row_token = b.take<int32_t>(2 * (size_t)p.max_rows + (size_t)p.S);
     p.rt.row_flat = p.rt.row_token ? p.rt.row_token + p.max_rows : nullptr;
-    p.row_tables_bytes = 2 * (size_t)p.max_rows * sizeof(int32_t);
+    p.rt.flat_row = p.rt.row_token ? p.rt.row_token + 2 * p.max_rows : nullptr;
+    p.row_tables_bytes = (2 * (size_t)p.max_rows + (size_t)p.S) * sizeof(int32_t);
     p.rt.row_weight = b.take<float>(p.max_rows);
   } else {
-    p.rt.row_token = p.rt.row_flat = nullptr;
+    p.rt.row_token = p.rt.row_flat = p.rt.flat_row = nullptr;
     p.rt.row_weight = nullptr;
   }
 }
@@ -98,7 +103,14 @@ static Plan plan_forward(void* ws, int64_t T, int H, int E, int K, int dtype) {
   carve_tables(b, p, T, E, K, true);
   p.xs = b.take<char>((size_t)p.max_rows * H * p.esize);
   p.act = b.take<char>((size_t)p.max_rows * H * p.esize);
-  if (dtype == YAMOE_BF16) p.acc32 = b.take<float>((size_t)T * H);
+  if (dtype == YAMOE_BF16) {
+    // decode path: fp32 accumulator [T,H]; grouped-GEMM path: weighted rows [max_rows,H].
+    // They are never live together, the larger one sizes the region.
+    const size_t a = (size_t)T * H * sizeof(float), y = (size_t)p.max_rows * H * p.esize;
+    char* region = b.take<char>(a > y ? a : y);
+    p.acc32 = reinterpret_cast<float*>(region);
+    p.yrows = region;
+  }
   p.slab_done = b.take<int32_t>((size_t)ceil_div(H, 64));
   p.bytes = b.off + 256;
   return p;
@@ -155,7 +167,8 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
                                  p.slab_done, st);
     if (rc != YAMOE_ERR_UNSUPPORTED) return rc;
   }
-  YB_CUDA_OK(cudaMemsetAsync(acc, 0, (size_t)Tn * H * sizeof(float), st));
+  const bool tc = use_tcgen05(path, dtype, H);
+  if (!tc) YB_CUDA_OK(cudaMemsetAsync(acc, 0, (size_t)Tn * H * sizeof(float), st));
 
   int rc = prepare_routing(p, st);
   if (rc) return rc;
@@ -176,19 +189,27 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
   EpiScatterAdd<T, true, true> comb{reinterpret_cast<const T*>(bd), acc, p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g1{p.xs, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, E,
               p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  g1.pair_expert = p.rt.pair_expert; g1.pair_off = p.rt.pair_off;
   GemmArgs g2{p.act, H, wd, H, (int64_t)H * H, 0, H, H, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  if (use_tcgen05(path, dtype, H)) {
+  g2.pair_expert = p.rt.pair_expert; g2.pair_off = p.rt.pair_off;
+  if (tc) {
     if constexpr (sizeof(T) == 2) {
       {
         StageTimer tm(kStageGateUp, st);
         rc = launch_umma_gemm<kFwd>(g1, glu, p.max_rows, p.max_tiles, st);
       }
       if (rc) return rc;
+      // two-step combine: weighted rows out of the GEMM epilogue, then one gather-sum pass
+      EpiWeightedRows<T> wrows{reinterpret_cast<const T*>(bd), reinterpret_cast<T*>(p.yrows), p.rt.row_token,
+                               p.rt.row_weight, H};
       {
         StageTimer tm(kStageDown, st);
-        rc = launch_umma_gemm<kFwd>(g2, comb, p.max_rows, p.max_tiles, st);
+        rc = launch_umma_gemm<kFwd>(g2, wrows, p.max_rows, p.max_tiles, st);
       }
       if (rc) return rc;
+      combine_padded_kernel<T><<<(unsigned)ceil_div(Tn, kRowWarps), kRowWarps * 32, 0, st>>>(
+          reinterpret_cast<const T*>(p.yrows), p.rt.flat_row, reinterpret_cast<T*>(out), Tn, H, K);
+      return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
     }
   } else {
     {
@@ -244,20 +265,25 @@ static int backward_impl(const void* grad_out, int per_slot, const void* hidden,
                 reinterpret_cast<T*>(p.pre), p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g1{p.xs, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, E,
               p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  g1.pair_expert = p.rt.pair_expert; g1.pair_off = p.rt.pair_off;
   // 2. gI' = gys W_d^T; fused GLU backward -> gpre, routing-weight gradient -> gw_row
   EpiGluBackward<T> glub{reinterpret_cast<const T*>(p.pre), reinterpret_cast<T*>(p.gpre), p.gw_row,
                          p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g2{p.gys, H, wd, H, (int64_t)H * H, 0, H, H, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  g2.pair_expert = p.rt.pair_expert; g2.pair_off = p.rt.pair_off;
   // 3. dW_d[e] = actw_e^T gys_e
   EpiStore<T> st_wd{reinterpret_cast<T*>(d_wd), H, H};
   GemmArgs g3{p.actw, H, p.gys, H, 0, H, H, 0, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  g3.pair_expert = p.rt.pair_expert; g3.pair_off = p.rt.pair_off;
   // 4. dHidden[token] += gpre W_gu^T
   EpiScatterAdd<T, false, false> sc_dh{nullptr, acc, p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g4{p.gpre, 2 * (int64_t)H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, H, 2 * H, E,
               p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  g4.pair_expert = p.rt.pair_expert; g4.pair_off = p.rt.pair_off;
   // 5. dW_gu[e] = xs_e^T gpre_e
   EpiStore<T> st_wgu{reinterpret_cast<T*>(d_wgu), H, 2 * H};
   GemmArgs g5{p.xs, H, p.gpre, 2 * (int64_t)H, 0, H, 2 * H, 0, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  g5.pair_expert = p.rt.pair_expert; g5.pair_off = p.rt.pair_off;
 
   if (use_tcgen05(path, dtype, H)) {
     if constexpr (sizeof(T) == 2) {
@@ -297,10 +323,14 @@ __global__ void uniform_tables_kernel(RouteTables rt, int E, int C) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i <= E) rt.pad_off[i] = i * C;
   if (i < E) rt.counts[i] = C;
-  if (i < E * (C / kTileM)) rt.tile_expert[i] = i / (C / kTileM);
+  const int tiles = C / kTileM, pairs = (tiles + 1) / 2;
+  if (i < E * tiles) rt.tile_expert[i] = i / tiles;
+  if (i <= E) rt.pair_off[i] = i * pairs;
+  if (i < E * pairs) rt.pair_expert[i] = i / pairs;
   if (i == 0) {
-    rt.header[kHdrRowTiles] = E * (C / kTileM);
+    rt.header[kHdrRowTiles] = E * tiles;
     rt.header[kHdrRowsUsed] = E * C;
+    rt.header[kHdrPairs] = E * pairs;
   }
 }
 
@@ -320,16 +350,19 @@ static int batch_mm_impl(const void* x, const void* w, void* out, int E, int C, 
   if (mode == kWgrad) {
     EpiStore<T> epi{reinterpret_cast<T*>(out), M, N};
     GemmArgs g{x, M, w, N, 0, M, N, 0, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+      g.pair_expert = p.rt.pair_expert; g.pair_off = p.rt.pair_off;
     if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma_gemm<kWgrad>(g, epi, rows, rows / kTileM, st); }
     else launch_simt_gemm<T, kWgrad>(g, epi, rows, st);
   } else {
     EpiStoreRows<T> epi{reinterpret_cast<T*>(out), N};
     if (mode == kFwd) {
       GemmArgs g{x, K, w, N, (int64_t)K * N, 0, N, K, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+      g.pair_expert = p.rt.pair_expert; g.pair_off = p.rt.pair_off;
       if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma_gemm<kFwd>(g, epi, rows, rows / kTileM, st); }
       else launch_simt_gemm<T, kFwd>(g, epi, rows, st);
     } else {
       GemmArgs g{x, K, w, K, (int64_t)K * N, 0, N, K, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+      g.pair_expert = p.rt.pair_expert; g.pair_off = p.rt.pair_off;
       if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma_gemm<kDgrad>(g, epi, rows, rows / kTileM, st); }
       else launch_simt_gemm<T, kDgrad>(g, epi, rows, st);
     }
@@ -437,6 +470,7 @@ int yamoe_b200_route(const int64_t* router_indices, int32_t* sorted_values, int3
   p.rt.bins = bins;
   if (counts) p.rt.counts = counts;
   p.rt.tile_expert = nullptr;
+  p.rt.pair_expert = nullptr;
   YB_CUDA_OK(cudaMemsetAsync(p.rt.header, 0, 16 * sizeof(int32_t), st));
   if (T == 0) {
     YB_CUDA_OK(cudaMemsetAsync(bins, 0, (size_t)(E + 1) * sizeof(int32_t), st));
