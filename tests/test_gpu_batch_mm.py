@@ -53,3 +53,32 @@ def test_batch_mm_fp32():
     out = torch.empty(2, 128, 128, device="cuda")
     yamoe_b200.batch_mm(x.cuda(), w.cuda(), torch.empty(0, device="cuda"), out, False)
     orc.check_close(out.cpu(), torch.bmm(x, w), 1e-5, "batch_mm fp32")
+
+
+def test_two_cta_kernel_in_subprocess():
+    """The cta_group::2 variant is selected by an environment variable read once per process."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch, yamoe_b200\n"
+        "from yamoe_b200 import workloads\n"
+        "from oracle import experts_oracle as orc\n"
+        "g = torch.Generator().manual_seed(0)\n"
+        "x = (torch.randn(3, 384, 320, generator=g) * 0.25).bfloat16(); w = (torch.randn(3, 320, 448, generator=g) * 0.25).bfloat16()\n"
+        "out = torch.empty(3, 384, 448, dtype=torch.bfloat16, device='cuda')\n"
+        "yamoe_b200.batch_mm(x.cuda(), w.cuda(), torch.empty(0, device='cuda'), out, False)\n"
+        "orc.check_close(out.float().cpu(), torch.bmm(x.float(), w.float()), 1e-2, 'two-CTA batch_mm')\n"
+        "wt = w.transpose(1, 2).contiguous()\n"
+        "yamoe_b200.batch_mm(x.cuda(), wt.cuda(), torch.empty(0, device='cuda'), out, True)\n"
+        "orc.check_close(out.float().cpu(), torch.bmm(x.float(), w.float()), 1e-2, 'two-CTA batch_mm trans_b')\n"
+        "keys = ['hidden_states','router_indices','routing_weights','gate_up_proj','gate_up_proj_bias','down_proj','down_proj_bias']\n"
+        "inp = workloads.make_inputs(700, 256, 8, 2, seed=4, weight_std=0.1, bias_std=0.2, dtype=torch.bfloat16)\n"
+        "o = yamoe_b200.experts(*[inp[k].cuda() for k in keys], 700, 8, 2)\n"
+        "ref = orc.experts_forward_oracle(*[inp[k] for k in keys], 700, 8, 2)\n"
+        "orc.check_close(o.float().cpu(), ref, 2e-2, 'two-CTA forward', rel_l2=1e-2)\n"
+        "print('ok')\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, YAMOE_B200_2CTA="1", PYTHONPATH=root)
+    res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

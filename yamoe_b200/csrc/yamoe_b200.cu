@@ -14,6 +14,7 @@
 #include "routing.cuh"
 #include "simt_gemm.cuh"
 #include "umma_gemm.cuh"
+#include "umma_gemm_2cta.cuh"
 #include "gemv.cuh"
 
 namespace yb {
@@ -196,7 +197,7 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
     if constexpr (sizeof(T) == 2) {
       {
         StageTimer tm(kStageGateUp, st);
-        rc = launch_umma_gemm<kFwd>(g1, glu, p.max_rows, p.max_tiles, st);
+        rc = launch_umma<kFwd>(g1, glu, p.max_rows, p.max_tiles, st);
       }
       if (rc) return rc;
       // two-step combine: weighted rows out of the GEMM epilogue, then one gather-sum pass
@@ -204,7 +205,7 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
                                p.rt.row_weight, H};
       {
         StageTimer tm(kStageDown, st);
-        rc = launch_umma_gemm<kFwd>(g2, wrows, p.max_rows, p.max_tiles, st);
+        rc = launch_umma<kFwd>(g2, wrows, p.max_rows, p.max_tiles, st);
       }
       if (rc) return rc;
       combine_padded_kernel<T><<<(unsigned)ceil_div(Tn, kRowWarps), kRowWarps * 32, 0, st>>>(
@@ -287,11 +288,11 @@ static int backward_impl(const void* grad_out, int per_slot, const void* hidden,
 
   if (use_tcgen05(path, dtype, H)) {
     if constexpr (sizeof(T) == 2) {
-      if ((rc = launch_umma_gemm<kFwd>(g1, glu, p.max_rows, p.max_tiles, st))) return rc;
-      if ((rc = launch_umma_gemm<kDgrad>(g2, glub, p.max_rows, p.max_tiles, st))) return rc;
-      if ((rc = launch_umma_gemm<kWgrad>(g3, st_wd, p.max_rows, p.max_tiles, st))) return rc;
-      if ((rc = launch_umma_gemm<kDgrad>(g4, sc_dh, p.max_rows, p.max_tiles, st))) return rc;
-      if ((rc = launch_umma_gemm<kWgrad>(g5, st_wgu, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma<kFwd>(g1, glu, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma<kDgrad>(g2, glub, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma<kWgrad>(g3, st_wd, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma<kDgrad>(g4, sc_dh, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma<kWgrad>(g5, st_wgu, p.max_rows, p.max_tiles, st))) return rc;
     }
   } else {
     launch_simt_gemm<T, kFwd>(g1, glu, p.max_rows, st);
@@ -351,19 +352,19 @@ static int batch_mm_impl(const void* x, const void* w, void* out, int E, int C, 
     EpiStore<T> epi{reinterpret_cast<T*>(out), M, N};
     GemmArgs g{x, M, w, N, 0, M, N, 0, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
       g.pair_expert = p.rt.pair_expert; g.pair_off = p.rt.pair_off;
-    if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma_gemm<kWgrad>(g, epi, rows, rows / kTileM, st); }
+    if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma<kWgrad>(g, epi, rows, rows / kTileM, st); }
     else launch_simt_gemm<T, kWgrad>(g, epi, rows, st);
   } else {
     EpiStoreRows<T> epi{reinterpret_cast<T*>(out), N};
     if (mode == kFwd) {
       GemmArgs g{x, K, w, N, (int64_t)K * N, 0, N, K, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
       g.pair_expert = p.rt.pair_expert; g.pair_off = p.rt.pair_off;
-      if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma_gemm<kFwd>(g, epi, rows, rows / kTileM, st); }
+      if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma<kFwd>(g, epi, rows, rows / kTileM, st); }
       else launch_simt_gemm<T, kFwd>(g, epi, rows, st);
     } else {
       GemmArgs g{x, K, w, K, (int64_t)K * N, 0, N, K, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
       g.pair_expert = p.rt.pair_expert; g.pair_off = p.rt.pair_off;
-      if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma_gemm<kDgrad>(g, epi, rows, rows / kTileM, st); }
+      if (tc) { if constexpr (sizeof(T) == 2) rc = launch_umma<kDgrad>(g, epi, rows, rows / kTileM, st); }
       else launch_simt_gemm<T, kDgrad>(g, epi, rows, st);
     }
   }
