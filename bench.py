@@ -377,7 +377,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gptoss20b_fwd_t4096", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--traffic", type=float, default=1.269e9,
+    ap.add_argument("--traffic", type=float, default=1.268e9,
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (see profiles/)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

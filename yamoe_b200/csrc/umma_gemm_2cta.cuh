@@ -1,14 +1,12 @@
 // Two-CTA (cta_group::2) variant of the tcgen05 grouped GEMM for the row-tiled arrangements
 // (forward and data gradients).
 //
-// The one-CTA kernel (umma_gemm.cuh) saturates shared-memory bandwidth: per 128x256x16 MMA the
-// tensor core reads 12 KB of operands while TMA writes another 12 KB, about 24 KB per
-// instruction against roughly 128 B/clk.  Here a cluster of two CTAs computes a 256 x 256 tile:
-// each CTA stages its own 128 rows of A and HALF of the B tile (128 columns); one
-// tcgen05.mma.cta_group::2 issued by the leader CTA multiplies the pair's 256 rows by all 256
-// columns, each SM accumulating its own 128 rows in its own TMEM.  Per SM and instruction that
-// is 8 KB of operands read and 8 KB written.  No TMA multicast is used anywhere: each CTA loads
-// its own operands and only the completion signals cross the pair.
+// A cluster of two CTAs computes a 256 x 256 tile: each CTA stages its own 128 rows of A and
+// HALF of the B tile (128 columns); one tcgen05.mma.cta_group::2 issued by the leader CTA
+// multiplies the pair's 256 rows by all 256 columns, each SM accumulating its own 128 rows in its
+// own TMEM.  Per SM and 64-deep k-block that is 32 KB of TMA traffic instead of the 48 KB of the
+// one-CTA kernel.  No TMA multicast is used anywhere: each CTA loads its own operands and only
+// the completion signals cross the pair.
 //
 // Signals:  both producers post their transaction bytes on the LEADER's full barrier
 // (cp.async.bulk.tensor ... .cta_group::2 with the leader's barrier address); the leader's MMA
