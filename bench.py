@@ -50,6 +50,7 @@ WORKLOADS = {
     # expert-parallel when launched on N > 1 GPUs: tokens sharded by rows, experts contiguously
     "gptoss120b_prefill_t16384": dict(T=16384, H=2880, E=128, K=4, mode="fwd", skew=True, ep=True),
     "gptoss20b_fwd_t8192_ep": dict(T=8192, H=2880, E=32, K=4, mode="fwd", ep=True),
+    "gptoss20b_bwd_t8192_ep": dict(T=8192, H=2880, E=32, K=4, mode="bwd", ep=True),
     "readme_fp32_t512": dict(T=512, H=2880, E=8, K=2, mode="fwd", fp32=True),
 }
 
@@ -225,13 +226,17 @@ def run_ours(args):
         T_total = T
         lo, hi = rank * (T // world), (rank + 1) * (T // world)
         local_w = ep.shard_expert_weights(*dev[3:], rank, world)
-        inp = {k: (v[lo:hi] if k in KEYS[:3] else v) for k, v in inp.items()}
+        inp = {k: (v[lo:hi] if k in KEYS[:3] + ["grad_out"] else v) for k, v in inp.items()}
+        if grad_out is not None:
+            grad_out = grad_out[lo:hi].contiguous()
         dev = [dev[i][lo:hi].contiguous() for i in range(3)] + list(local_w)
         torch.cuda.empty_cache()
         T = hi - lo
         ep_stats = {}
 
     def step():
+        if use_ep and w["mode"] == "bwd":
+            return ep.ep_experts_backward(grad_out, *dev, cap, E, K)
         if use_ep:
             return ep.ep_experts(*dev, cap, E, K, stats=ep_stats)
         if w["mode"] == "bwd":
@@ -296,7 +301,8 @@ def run_ours(args):
         a = [x.to("cuda", non_blocking=True) for x in host_in]
         if w["mode"] == "bwd":
             g = host_go.to("cuda", non_blocking=True)
-            outs = yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K)
+            outs = (ep.ep_experts_backward(g, *a, *dev[3:], cap, E, K) if use_ep
+                    else yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K))
             host_out.copy_(outs[0], non_blocking=True)
         elif use_ep:
             out = ep.ep_experts(*a, *dev[3:], cap, E, K)
@@ -322,7 +328,7 @@ def run_ours(args):
 
     if rank == 0:
         peaks = measured_peaks()
-        S = ep_stats["rows_received"] if use_ep else T * K      # rows this rank's GEMMs process
+        S = ep_stats.get("rows_received", T * K) if use_ep else T * K      # rows this rank's GEMMs process
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,

@@ -41,7 +41,11 @@ def cpu_backend():
             out[ok] += w[ok, k, None].double() * rows[pos[ok]].double()
         return out.to(rows.dtype)
 
-    return ep.Backend(route=route, permute_rows=permute_rows, experts=experts, combine_rows=combine_rows)
+    def experts_backward(*a):
+        return [g.to(a[1].dtype) for g in orc.experts_backward_oracle(*a)]
+
+    return ep.Backend(route=route, permute_rows=permute_rows, experts=experts, combine_rows=combine_rows,
+                      experts_backward=experts_backward)
 
 
 def _worker(rank, world, port, T, H, E, K, cap, skew, q):
@@ -52,12 +56,16 @@ def _worker(rank, world, port, T, H, E, K, cap, skew, q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from yamoe_b200 import ep, workloads
-        inp = workloads.make_inputs(T, H, E, K, seed=5, weight_std=0.3, bias_std=0.3, skew=skew)
+        inp = workloads.make_inputs(T, H, E, K, seed=5, weight_std=0.3, bias_std=0.3, skew=skew, with_grad=True)
         lo, hi = rank * (T // world), (rank + 1) * (T // world)
         local_w = ep.shard_expert_weights(*[inp[k] for k in KEYS[3:]], rank, world)
         stats = {}
         out = ep.ep_experts(inp["hidden_states"][lo:hi], inp["router_indices"][lo:hi], inp["routing_weights"][lo:hi],
                             *local_w, cap, E, K, backend=cpu_backend(), stats=stats)
+        grads = ep.ep_experts_backward(inp["grad_out"][lo:hi], inp["hidden_states"][lo:hi],
+                                       inp["router_indices"][lo:hi], inp["routing_weights"][lo:hi], *local_w, cap, E, K,
+                                       backend=cpu_backend())
+        stats["grads"] = grads
         q.put((rank, out, stats))
         dist.barrier()
     except Exception as exc:  # surface the failure instead of letting the parent time out
@@ -88,10 +96,15 @@ def test_ep_matches_single_process(world, T, H, E, K, cap, skew):
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    inp = workloads.make_inputs(T, H, E, K, seed=5, weight_std=0.3, bias_std=0.3, skew=skew)
+    inp = workloads.make_inputs(T, H, E, K, seed=5, weight_std=0.3, bias_std=0.3, skew=skew, with_grad=True)
     ref = orc.experts_forward_oracle(*[inp[k] for k in KEYS], cap, E, K)
     got = torch.cat([r[1] for r in results])
     orc.check_close(got, ref, 1e-5, "expert-parallel vs single process")
+    # backward: token-sharded gradients concatenate over ranks, expert-sharded ones over experts
+    ref_g = orc.experts_backward_oracle(inp["grad_out"], *[inp[k] for k in KEYS], cap, E, K)
+    for i, name in enumerate(["d_hidden", "d_routing", "d_wgu", "d_bgu", "d_wd", "d_bd"]):
+        got_g = torch.cat([r[2]["grads"][i] for r in results])
+        orc.check_close(got_g, ref_g[i], 2e-5, f"expert-parallel {name}")
     # conservation: every row sent is received by exactly one rank
     assert sum(r[2]["rows_sent"] for r in results) == sum(r[2]["rows_received"] for r in results) == T * K
     if cap < T:

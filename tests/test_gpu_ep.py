@@ -21,14 +21,18 @@ def _worker(rank, world, port, T, H, E, K, cap, skew, q):
     try:
         import yamoe_b200
         from yamoe_b200 import ep, workloads
-        inp = workloads.make_inputs(T, H, E, K, seed=9, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16, skew=skew)
+        inp = workloads.make_inputs(T, H, E, K, seed=9, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16, skew=skew,
+                                    with_grad=True)
         lo, hi = rank * (T // world), (rank + 1) * (T // world)
         local_w = ep.shard_expert_weights(*[inp[k].cuda() for k in KEYS[3:]], rank, world)
         out = ep.ep_experts(inp["hidden_states"][lo:hi].cuda(), inp["router_indices"][lo:hi].cuda(),
                             inp["routing_weights"][lo:hi].cuda(), *local_w, cap, E, K)
         single = yamoe_b200.experts(*[inp[k].cuda() for k in KEYS], cap, E, K)[lo:hi]
+        grads = ep.ep_experts_backward(inp["grad_out"][lo:hi].cuda(), inp["hidden_states"][lo:hi].cuda(),
+                                       inp["router_indices"][lo:hi].cuda(), inp["routing_weights"][lo:hi].cuda(),
+                                       *local_w, cap, E, K)
         torch.cuda.synchronize()
-        q.put((rank, out.float().cpu(), single.float().cpu()))
+        q.put((rank, out.float().cpu(), (single.float().cpu(), [g.float().cpu() for g in grads])))
         dist.barrier()
     except Exception as exc:
         q.put((rank, repr(exc), None))
@@ -60,11 +64,16 @@ def test_ep_two_gpus_matches_single_gpu(T, H, E, K, cap, skew):
         p.join(timeout=60)
     results.sort(key=lambda x: x[0])
     got = torch.cat([r[1] for r in results])
-    single = torch.cat([r[2] for r in results])
-    inp = workloads.make_inputs(T, H, E, K, seed=9, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16, skew=skew)
+    single = torch.cat([r[2][0] for r in results])
+    inp = workloads.make_inputs(T, H, E, K, seed=9, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16, skew=skew,
+                                with_grad=True)
     ref = orc.experts_forward_oracle(*[inp[k] for k in KEYS], cap, E, K)
     orc.check_close(got, ref, 2e-2, "expert-parallel vs oracle", rel_l2=1e-2)
     orc.check_close(got, single, 2e-2, "expert-parallel vs single-GPU op", rel_l2=1e-2)
+    ref_g = orc.experts_backward_oracle(inp["grad_out"], *[inp[k] for k in KEYS], cap, E, K)
+    for i, name in enumerate(["d_hidden", "d_routing", "d_wgu", "d_bgu", "d_wd", "d_bd"]):
+        got_g = torch.cat([r[2][1][i] for r in results])
+        orc.check_close(got_g, ref_g[i], 2e-2, f"expert-parallel {name}", rel_l2=2e-2)
 
 
 def test_permute_and_combine_rows_single_gpu():

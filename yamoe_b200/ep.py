@@ -38,12 +38,13 @@ class Backend:
     permute_rows: Callable  # (hidden [T,H], sorted_indices, K) -> rows [S,H]
     experts: Callable      # the expert op
     combine_rows: Callable  # (rows [S,H], sorted_indices, router_indices, routing_weights, E) -> [T,H]
+    experts_backward: Optional[Callable] = None   # the backward op
 
 
 def cuda_backend() -> Backend:
     from . import ops
     return Backend(route=ops.route, permute_rows=ops.permute_rows, experts=ops.experts,
-                   combine_rows=ops.combine_rows)
+                   combine_rows=ops.combine_rows, experts_backward=ops.experts_backward)
 
 
 def expert_range(rank: int, world: int, num_experts: int):
@@ -110,3 +111,63 @@ def ep_experts(hidden_states, router_indices, routing_weights, gate_up_local, ga
     if stats is not None:
         stats.update(rows_sent=n_send, rows_received=n_recv, send_splits=send_splits, recv_splits=recv_splits)
     return out
+
+
+def ep_experts_backward(grad_out, hidden_states, router_indices, routing_weights, gate_up_local,
+                        gate_up_bias_local, down_local, down_bias_local, expert_capacity: int, num_experts: int,
+                        top_k: int, group=None, backend: Optional[Backend] = None):
+    """Expert-parallel `experts_backward`.  Same sharding as `ep_experts`; `grad_out` is this rank's
+    [T_r, H] slice.  The exchange mirrors the forward: token rows, their upstream-gradient rows and
+    their routing weights travel to the expert owners, which run the backward op on a local problem
+    with top_k = 1; per-row input gradients and routing-weight gradients travel back.  Weight and
+    bias gradients stay with the expert owner (experts are not replicated, so no all-reduce).
+
+    Returns (d_hidden [T_r,H], d_routing [T_r, cols], d_gate_up_local, d_gate_up_bias_local,
+    d_down_local, d_down_bias_local)."""
+    be = backend or cuda_backend()
+    world = dist.get_world_size(group)
+    E, K = int(num_experts), int(top_k)
+    per = E // world
+    T, H = hidden_states.shape
+    dt, dev = hidden_states.dtype, hidden_states.device
+
+    _, sorted_indices, _, counts = be.route(router_indices, E)
+    recv_counts, send_splits, recv_splits = exchange_plan(counts, world, group)
+    n_send, n_recv = sum(send_splits), sum(recv_splits)
+    sorted_indices = sorted_indices[:n_send]
+    si = sorted_indices.long()
+
+    dense = routing_weights.shape[1] == E
+    w_sel = torch.gather(routing_weights, 1, router_indices.to(torch.int64)) if dense else routing_weights
+    rows_x = be.permute_rows(hidden_states, sorted_indices, K)
+    rows_g = be.permute_rows(grad_out.reshape(T, H), sorted_indices, K)
+    rows_w = w_sel.reshape(-1)[si].reshape(n_send, 1).contiguous()
+
+    def exchange(t, out_rows, out_splits, in_splits):
+        buf = torch.empty(out_rows, t.shape[1], dtype=t.dtype, device=t.device)
+        dist.all_to_all_single(buf, t.contiguous(), out_splits, in_splits, group=group)
+        return buf
+
+    recv_x = exchange(rows_x, n_recv, recv_splits, send_splits)
+    recv_g = exchange(rows_g, n_recv, recv_splits, send_splits)
+    recv_w = exchange(rows_w, n_recv, recv_splits, send_splits)
+    local_ids = torch.repeat_interleave(
+        torch.arange(per, device=dev).repeat(world), recv_counts.view(-1).to(dev), output_size=n_recv).view(n_recv, 1)
+
+    d_rows, d_w_rows, d_wgu, d_bgu, d_wd, d_bd = be.experts_backward(
+        recv_g, recv_x, local_ids, recv_w, gate_up_local, gate_up_bias_local, down_local, down_bias_local,
+        int(expert_capacity), per, 1)
+
+    back_rows = exchange(d_rows, n_send, send_splits, recv_splits)
+    back_w = exchange(d_w_rows.reshape(n_recv, 1), n_send, send_splits, recv_splits)
+
+    ones = torch.ones(T, K, dtype=dt, device=dev)
+    d_hidden = be.combine_rows(back_rows, sorted_indices, router_indices, ones, E)
+    d_sel = torch.zeros(T * K, dtype=dt, device=dev)
+    d_sel[si] = back_w.reshape(-1)
+    if dense:
+        d_routing = torch.zeros(T, E, dtype=dt, device=dev)
+        d_routing.scatter_(1, router_indices.to(torch.int64), d_sel.view(T, K))
+    else:
+        d_routing = d_sel.view(T, K)
+    return d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd
