@@ -182,6 +182,37 @@ int yamoe_b200_combine_rows(const void *rows, const int32_t *sorted_indices, int
                             void *out, int64_t T, int H, int E, int K, int dtype, void *workspace,
                             size_t workspace_bytes, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Expert parallelism over peer memory (no counterpart in the reference).  G ranks, rank r owns
+ * experts [r*E/G, (r+1)*E/G).  `peer_recv` / `peer_back` are DEVICE arrays of G pointers to
+ * buffers every rank allocated with the same size and made peer-accessible:
+ *   recv  [max_rows, H]  rows this rank's experts receive, in the padded expert-sorted layout
+ *   back  [S_max, H]     result rows of this rank's own assignments, in its sorted order
+ * max_rows must be a multiple of 128 and at least (total assignments of all ranks) + 128*E/G.
+ * One forward call is, on every rank and on one stream:
+ *   yamoe_b200_route            local stable sort -> sorted_values, sorted_indices, bins, counts
+ *   (all-gather of counts)      -> counts_all [G, E] on the device
+ *   yamoe_b200_ep_plan          offsets, local tile tables and row validity, all on the device
+ *   yamoe_b200_ep_dispatch      hidden rows -> owner's recv buffer (peer stores)
+ *   (any stream-ordered collective as a barrier)
+ *   yamoe_b200_ep_local_forward gate_up + GLU + down on the received rows -> y_rows [max_rows, H]
+ *   yamoe_b200_ep_return        y rows -> source rank's back buffer (peer stores; zeros if dropped)
+ *   (barrier)                   then yamoe_b200_combine_rows on `back`
+ * No host synchronisation and no host-side split sizes are involved.  The kernels only store
+ * to peer memory; none of them reads from or waits on another GPU.
+ * ------------------------------------------------------------------------------------------- */
+size_t yamoe_b200_ep_workspace_bytes(int64_t max_rows, int H, int E, int G, int dtype);
+int yamoe_b200_ep_plan(const int32_t *counts_all, int G, int rank, int E, int64_t expert_capacity,
+                       int64_t max_rows, int H, int dtype, void *workspace, size_t workspace_bytes, void *stream);
+int yamoe_b200_ep_dispatch(const void *hidden_states, const int32_t *sorted_values, const int32_t *sorted_indices,
+                           const int32_t *bins, int64_t S, void *const *peer_recv, int64_t max_rows, int H, int E,
+                           int G, int K, int dtype, const void *workspace, void *stream);
+int yamoe_b200_ep_local_forward(const void *recv_x, const void *gate_up_proj, const void *gate_up_proj_bias,
+                                const void *down_proj, const void *down_proj_bias, void *y_rows, int64_t max_rows,
+                                int H, int E, int G, int dtype, void *workspace, void *stream);
+int yamoe_b200_ep_return(const void *y_rows, void *const *peer_back, int64_t max_rows, int H, int E, int G,
+                         int dtype, const void *workspace, void *stream);
+
 /* Device status word of the last forward/backward call that used `workspace`: 0 when every
  * bounded device-side wait completed, otherwise a code naming the wait that gave up.  Reads
  * 4 bytes from the device with cudaMemcpyAsync on `stream` and synchronises that stream. */

@@ -95,3 +95,63 @@ def test_permute_and_combine_rows_single_gpu():
         # assignments missing from the sorted list contribute nothing
         half = ops.combine_rows(rows[: si.numel() // 2], si[: si.numel() // 2], ri, rw, E)
         assert half.float().abs().sum() < out.float().abs().sum()
+
+
+def _peer_worker(rank, world, port, q):
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from yamoe_b200 import ep, workloads
+        outs = []
+        H, E, K = 256, 16, 4
+        ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=1024, max_tokens_local=512, dtype=torch.bfloat16)
+        # three calls in a row on the same buffers: full capacity, a dropping capacity, fewer tokens
+        for T, cap, skew, seed in ((1024, 1024, False, 9), (1024, 100, True, 10), (512, 512, True, 11)):
+            inp = workloads.make_inputs(T, H, E, K, seed=seed, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16,
+                                        skew=skew)
+            lo, hi = rank * (T // world), (rank + 1) * (T // world)
+            local_w = ep.shard_expert_weights(*[inp[k].cuda() for k in KEYS[3:]], rank, world)
+            out = ctx.forward(inp["hidden_states"][lo:hi].cuda(), inp["router_indices"][lo:hi].cuda(),
+                              inp["routing_weights"][lo:hi].cuda(), *local_w, cap)
+            torch.cuda.synchronize()
+            outs.append(out.float().cpu())
+        q.put((rank, outs, True))
+        dist.barrier()
+    except Exception as exc:
+        q.put((rank, repr(exc), None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_store_ep_two_gpus():
+    """Dispatch and combine as peer stores with on-device offsets (no host round trip)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from oracle import experts_oracle as orc
+    from yamoe_b200 import workloads
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29800 + os.getpid() % 1000
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(2)]
+    bad = [r for r in results if r[2] is None]
+    if bad:
+        for p in procs:
+            p.terminate()
+        pytest.fail(f"rank {bad[0][0]}: {bad[0][1]}")
+    for p in procs:
+        p.join(timeout=60)
+    results.sort(key=lambda x: x[0])
+    H, E, K = 256, 16, 4
+    for i, (T, cap, skew, seed) in enumerate(((1024, 1024, False, 9), (1024, 100, True, 10), (512, 512, True, 11))):
+        inp = workloads.make_inputs(T, H, E, K, seed=seed, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16, skew=skew)
+        ref = orc.experts_forward_oracle(*[inp[k] for k in KEYS], cap, E, K)
+        got = torch.cat([r[1][i] for r in results])
+        orc.check_close(got, ref, 2e-2, f"peer-store expert parallel, call {i}", rel_l2=1e-2)

@@ -16,6 +16,7 @@
 #include "umma_gemm.cuh"
 #include "umma_gemm_2cta.cuh"
 #include "gemv.cuh"
+#include "ep_p2p.cuh"
 
 namespace yb {
 
@@ -372,6 +373,78 @@ static int batch_mm_impl(const void* x, const void* w, void* out, int E, int C, 
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
+// ---- expert parallelism over peer memory ---------------------------------------------------
+struct EpPlan {
+  EpTables t;
+  void* act = nullptr;     // [max_rows, H]
+  size_t bytes = 0;
+};
+
+static EpPlan plan_ep(void* ws, int64_t max_rows, int H, int E, int G, int dtype) {
+  EpPlan p;
+  Bump b(ws);
+  const int per = E / G;
+  const int64_t max_tiles = max_rows / kTileM;
+  RouteTables& rt = p.t.rt;
+  rt = RouteTables{};
+  rt.header = b.take<int32_t>(16);
+  rt.counts = b.take<int32_t>(per);
+  rt.bins = b.take<int32_t>(per + 1);
+  rt.pad_off = b.take<int32_t>(per + 1);
+  rt.pair_off = b.take<int32_t>(per + 1);
+  rt.tile_expert = b.take<int32_t>(max_tiles);
+  rt.pair_expert = b.take<int32_t>(max_tiles);
+  rt.row_token = b.take<int32_t>(max_rows);
+  rt.row_weight = b.take<float>(max_rows);
+  p.t.dest_row = b.take<int32_t>(E);
+  p.t.src_start = b.take<int32_t>((size_t)G * per);
+  p.t.seg_row = b.take<int32_t>((size_t)G * per);
+  p.act = b.take<char>((size_t)max_rows * H * (dtype == YAMOE_BF16 ? 2 : 4));
+  p.bytes = b.off + 256;
+  return p;
+}
+
+static int check_ep(int64_t max_rows, int H, int E, int G, int rank, int dtype) {
+  if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
+  if (H <= 0 || H % 8 != 0 || E <= 0 || G <= 0 || G > 256 || E % G != 0 || rank < 0 || rank >= G) return YAMOE_ERR_BAD_ARG;
+  if (max_rows <= 0 || max_rows % kTileM != 0 || E > 1024) return YAMOE_ERR_BAD_ARG;
+  return YAMOE_OK;
+}
+
+template <typename T>
+static int ep_local_forward_impl(const void* recv_x, const void* wgu, const void* bgu, const void* wd,
+                                 const void* bd, void* yrows, int64_t max_rows, int H, int per, int dtype,
+                                 const EpPlan& p, cudaStream_t st) {
+  const RouteTables& rt = p.t.rt;
+  const int64_t max_tiles = max_rows / kTileM;
+  EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), reinterpret_cast<T*>(p.act), nullptr, nullptr, rt.row_token,
+                rt.row_weight, H};
+  EpiWeightedRows<T> wrows{reinterpret_cast<const T*>(bd), reinterpret_cast<T*>(yrows), rt.row_token,
+                           rt.row_weight, H};
+  GemmArgs g1{recv_x, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, per, rt.tile_expert, rt.pad_off,
+              rt.header};
+  g1.pair_expert = rt.pair_expert; g1.pair_off = rt.pair_off;
+  GemmArgs g2{p.act, H, wd, H, (int64_t)H * H, 0, H, H, per, rt.tile_expert, rt.pad_off, rt.header};
+  g2.pair_expert = rt.pair_expert; g2.pair_off = rt.pair_off;
+  int rc = YAMOE_OK;
+  if (use_tcgen05(current_path(), dtype, H)) {
+    if constexpr (sizeof(T) == 2) {
+      {
+        StageTimer tm(kStageGateUp, st);
+        rc = launch_umma<kFwd>(g1, glu, max_rows, max_tiles, st);
+      }
+      if (rc) return rc;
+      StageTimer tm(kStageDown, st);
+      rc = launch_umma<kFwd>(g2, wrows, max_rows, max_tiles, st);
+      if (rc) return rc;
+    }
+  } else {
+    launch_simt_gemm<T, kFwd>(g1, glu, max_rows, st);
+    launch_simt_gemm<T, kFwd>(g2, wrows, max_rows, st);
+  }
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
 // ---- routing without a caller workspace -------------------------------------------------
 // Scratch for yamoe_b200_route_static.  It is part of the library image: every GPU that loads the
 // library keeps these bytes reserved until the process exits.  All calls on one device share it.
@@ -647,6 +720,82 @@ int yamoe_b200_combine_rows(const void* rows, const int32_t* sorted_indices, int
     combine_rows_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(
         reinterpret_cast<const float*>(rows), inv, router_indices, reinterpret_cast<const float*>(routing_weights),
         routing_cols, reinterpret_cast<float*>(out), T, H, E, K);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+size_t yamoe_b200_ep_workspace_bytes(int64_t max_rows, int H, int E, int G, int dtype) {
+  if (check_ep(max_rows, H, E, G, 0, dtype)) return 0;
+  return plan_ep(nullptr, max_rows, H, E, G, dtype).bytes;
+}
+
+int yamoe_b200_ep_plan(const int32_t* counts_all, int G, int rank, int E, int64_t expert_capacity,
+                       int64_t max_rows, int H, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_ep(max_rows, H, E, G, rank, dtype);
+  if (rc) return rc;
+  if (!counts_all || expert_capacity < 0) return YAMOE_ERR_BAD_ARG;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < yamoe_b200_ep_workspace_bytes(max_rows, H, E, G, dtype))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  EpPlan p = plan_ep(workspace, max_rows, H, E, G, dtype);
+  YB_CUDA_OK(cudaMemsetAsync(p.t.rt.header, 0, 16 * sizeof(int32_t), st));
+  ep_plan_kernel<<<1, 256, (size_t)3 * E * sizeof(int32_t), st>>>(counts_all, G, rank, E, p.t);
+  ep_rowtables_kernel<<<(unsigned)ceil_div(max_rows, 256), 256, 0, st>>>(p.t, expert_capacity, max_rows);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+int yamoe_b200_ep_dispatch(const void* hidden_states, const int32_t* sorted_values, const int32_t* sorted_indices,
+                           const int32_t* bins, int64_t S, void* const* peer_recv, int64_t max_rows, int H, int E,
+                           int G, int K, int dtype, const void* workspace, void* stream) {
+  int rc = check_ep(max_rows, H, E, G, 0, dtype);
+  if (rc) return rc;
+  if (S == 0) return YAMOE_OK;
+  if (!hidden_states || !sorted_values || !sorted_indices || !bins || !peer_recv || !workspace || K <= 0 || S < 0)
+    return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  EpPlan p = plan_ep(const_cast<void*>(workspace), max_rows, H, E, G, dtype);
+  const unsigned blocks = (unsigned)ceil_div(S, kRowWarps);
+  if (dtype == YAMOE_BF16)
+    ep_dispatch_kernel<__nv_bfloat16><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(hidden_states), sorted_values, sorted_indices, bins, p.t.dest_row,
+        peer_recv, S, H, E, E / G, K);
+  else
+    ep_dispatch_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const float*>(hidden_states), sorted_values, sorted_indices, bins, p.t.dest_row, peer_recv,
+        S, H, E, E / G, K);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+int yamoe_b200_ep_local_forward(const void* recv_x, const void* gate_up_proj, const void* gate_up_proj_bias,
+                                const void* down_proj, const void* down_proj_bias, void* y_rows, int64_t max_rows,
+                                int H, int E, int G, int dtype, void* workspace, void* stream) {
+  int rc = check_ep(max_rows, H, E, G, 0, dtype);
+  if (rc) return rc;
+  if (!recv_x || !gate_up_proj || !gate_up_proj_bias || !down_proj || !down_proj_bias || !y_rows || !workspace)
+    return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  EpPlan p = plan_ep(workspace, max_rows, H, E, G, dtype);
+  if (dtype == YAMOE_BF16)
+    return ep_local_forward_impl<__nv_bfloat16>(recv_x, gate_up_proj, gate_up_proj_bias, down_proj, down_proj_bias,
+                                                y_rows, max_rows, H, E / G, dtype, p, st);
+  return ep_local_forward_impl<float>(recv_x, gate_up_proj, gate_up_proj_bias, down_proj, down_proj_bias, y_rows,
+                                      max_rows, H, E / G, dtype, p, st);
+}
+
+int yamoe_b200_ep_return(const void* y_rows, void* const* peer_back, int64_t max_rows, int H, int E, int G,
+                         int dtype, const void* workspace, void* stream) {
+  int rc = check_ep(max_rows, H, E, G, 0, dtype);
+  if (rc) return rc;
+  if (!y_rows || !peer_back || !workspace) return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  EpPlan p = plan_ep(const_cast<void*>(workspace), max_rows, H, E, G, dtype);
+  const unsigned blocks = (unsigned)ceil_div(max_rows, kRowWarps);
+  if (dtype == YAMOE_BF16)
+    ep_return_kernel<__nv_bfloat16><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(y_rows), p.t, peer_back, H, G, E / G);
+  else
+    ep_return_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const float*>(y_rows), p.t,
+                                                              peer_back, H, G, E / G);
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 

@@ -171,3 +171,79 @@ def ep_experts_backward(grad_out, hidden_states, router_indices, routing_weights
     else:
         d_routing = d_sel.view(T, K)
     return d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd
+
+
+class PeerExpertParallel:
+    """Expert-parallel forward whose dispatch and combine are peer stores over NVLink.
+
+    All offsets come from the all-gathered [G, E] count matrix on the device: a call makes no
+    device-to-host copy and needs no split sizes.  Buffers that peers write into are symmetric
+    allocations made once, sized for `max_tokens_total` tokens over all ranks (worst case: every
+    assignment lands on one rank) and `max_tokens_local` tokens on this rank.
+
+    Sequence per call (one stream): route -> all_gather(counts) -> plan -> dispatch (peer stores) ->
+    barrier -> grouped GEMMs on the received rows -> return (peer stores) -> barrier -> combine.
+    The barriers are stream-ordered collectives; no kernel of this path waits on another GPU.
+    """
+
+    def __init__(self, hidden: int, num_experts: int, top_k: int, max_tokens_total: int, max_tokens_local: int,
+                 dtype=torch.bfloat16, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.H, self.E, self.K, self.dtype = int(hidden), int(num_experts), int(top_k), dtype
+        if self.E % self.world:
+            raise ValueError("num_experts must be divisible by the group size")
+        self.per = self.E // self.world
+        self.dt = _lib.YAMOE_BF16 if dtype == torch.bfloat16 else _lib.YAMOE_F32
+        s_total = max_tokens_total * self.K
+        self.max_rows = ((s_total + 127) // 128 + self.per) * 128
+        self.s_local = max_tokens_local * self.K
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.recv = symm_mem.empty(self.max_rows, self.H, dtype=dtype, device=dev)
+        self.back = symm_mem.empty(max(self.s_local, 1), self.H, dtype=dtype, device=dev)
+        h_recv = symm_mem.rendezvous(self.recv, self.group)
+        h_back = symm_mem.rendezvous(self.back, self.group)
+        self.peer_recv = torch.tensor(list(h_recv.buffer_ptrs), dtype=torch.int64, device=dev)
+        self.peer_back = torch.tensor(list(h_back.buffer_ptrs), dtype=torch.int64, device=dev)
+        self._handles = (h_recv, h_back)
+        self.L = _lib.lib()
+        nbytes = self.L.yamoe_b200_ep_workspace_bytes(self.max_rows, self.H, self.E, self.world, self.dt)
+        if nbytes == 0:
+            raise RuntimeError("yamoe_b200: unsupported expert-parallel configuration")
+        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.y_rows = torch.empty(self.max_rows, self.H, dtype=dtype, device=dev)
+        self.counts_all = torch.empty(self.world, self.E, dtype=torch.int32, device=dev)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._check = _lib.check
+
+    def _barrier(self):
+        dist.all_reduce(self.flag, group=self.group)      # stream-ordered; orders the peer stores
+
+    def forward(self, hidden_states, router_indices, routing_weights, gate_up_local, gate_up_bias_local,
+                down_local, down_bias_local, expert_capacity: int):
+        from . import ops
+        T, K = router_indices.shape
+        if T * K > self.s_local or K != self.K or hidden_states.shape[1] != self.H:
+            raise RuntimeError("PeerExpertParallel: call exceeds the sizes the buffers were made for")
+        L, st = self.L, torch.cuda.current_stream().cuda_stream
+        hs = hidden_states.contiguous()
+        sv, si, bins, counts = ops.route(router_indices, self.E)
+        dist.all_gather_into_tensor(self.counts_all.view(-1), counts, group=self.group)
+        self._check(L.yamoe_b200_ep_plan(self.counts_all.data_ptr(), self.world, self.rank, self.E,
+                                         int(expert_capacity), self.max_rows, self.H, self.dt, self.ws.data_ptr(),
+                                         self.ws.numel(), st), "ep_plan")
+        self._check(L.yamoe_b200_ep_dispatch(hs.data_ptr(), sv.data_ptr(), si.data_ptr(), bins.data_ptr(), T * K,
+                                             self.peer_recv.data_ptr(), self.max_rows, self.H, self.E, self.world, K,
+                                             self.dt, self.ws.data_ptr(), st), "ep_dispatch")
+        self._barrier()
+        self._check(L.yamoe_b200_ep_local_forward(self.recv.data_ptr(), gate_up_local.data_ptr(),
+                                                  gate_up_bias_local.data_ptr(), down_local.data_ptr(),
+                                                  down_bias_local.data_ptr(), self.y_rows.data_ptr(), self.max_rows,
+                                                  self.H, self.E, self.world, self.dt, self.ws.data_ptr(), st),
+                    "ep_local_forward")
+        self._check(L.yamoe_b200_ep_return(self.y_rows.data_ptr(), self.peer_back.data_ptr(), self.max_rows, self.H,
+                                           self.E, self.world, self.dt, self.ws.data_ptr(), st), "ep_return")
+        self._barrier()
+        return ops.combine_rows(self.back[: T * K], si, router_indices, routing_weights, self.E)
