@@ -233,10 +233,15 @@ def run_ours(args):
         torch.cuda.empty_cache()
         T = hi - lo
         ep_stats = {}
+        peer_ctx = None
+        if args.ep_mode == "peer" and w["mode"] == "fwd":
+            peer_ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=T_total, max_tokens_local=T, dtype=dtype)
 
     def step():
         if use_ep and w["mode"] == "bwd":
             return ep.ep_experts_backward(grad_out, *dev, cap, E, K)
+        if use_ep and peer_ctx is not None:
+            return peer_ctx.forward(*dev, cap)
         if use_ep:
             return ep.ep_experts(*dev, cap, E, K, stats=ep_stats)
         if w["mode"] == "bwd":
@@ -305,7 +310,7 @@ def run_ours(args):
                     else yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K))
             host_out.copy_(outs[0], non_blocking=True)
         elif use_ep:
-            out = ep.ep_experts(*a, *dev[3:], cap, E, K)
+            out = peer_ctx.forward(*a, *dev[3:], cap) if peer_ctx is not None else ep.ep_experts(*a, *dev[3:], cap, E, K)
             host_out.copy_(out, non_blocking=True)
         else:
             out = yamoe_b200.experts(*a, *dev[3:], cap, E, K)
@@ -328,6 +333,9 @@ def run_ours(args):
 
     if rank == 0:
         peaks = measured_peaks()
+        if use_ep and peer_ctx is not None:
+            per = E // world
+            ep_stats["rows_received"] = int(peer_ctx.counts_all[:, rank * per:(rank + 1) * per].sum().item())
         S = ep_stats.get("rows_received", T * K) if use_ep else T * K      # rows this rank's GEMMs process
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -337,9 +345,11 @@ def run_ours(args):
             "data": "synthetic (seeded, shapes of the reference's own benchmarks)",
             "config": {"workload": args.workload, "tokens": T, "hidden": H, "experts": E, "top_k": K,
                        "pass": w["mode"], "expert_capacity": cap,
-                       "parallelism": (f"ep{world} (tokens sharded by rows, experts sharded contiguously, NCCL all-to-all "
-                                       f"dispatch + combine; rank-0 rows sent/received {ep_stats.get('rows_sent')}/"
-                                       f"{ep_stats.get('rows_received')})") if use_ep else
+                       "parallelism": (f"ep{world} (tokens sharded by rows, experts sharded contiguously, "
+                                       + ("dispatch + combine as NVLink peer stores, offsets on device, no host sync)"
+                                          if use_ep and peer_ctx is not None else
+                                          "NCCL all-to-all dispatch + combine; rank-0 rows sent/received "
+                                          f"{ep_stats.get('rows_sent')}/{ep_stats.get('rows_received')})")) if use_ep else
                                       f"dp{world} (token shards, replicated experts, no collective)",
                        "l2": ("L2 flushed (256 MB write) between steps, each step timed by its own events" if decode
                               else f"expert weights ({weight_bytes / 1e9:.1f} GB) exceed the 126 MB L2; no flush")},
@@ -383,6 +393,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gptoss20b_fwd_t4096", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-mode", default="peer", choices=["peer", "nccl"],
+                    help="exchange used by the expert-parallel workloads on N > 1 GPUs")
     ap.add_argument("--traffic", type=float, default=1.268e9,
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (see profiles/)")
     args = ap.parse_args()
