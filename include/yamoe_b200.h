@@ -195,15 +195,20 @@ int yamoe_b200_combine_rows(const void *rows, const int32_t *sorted_indices, int
  *   yamoe_b200_ep_plan          offsets, local tile tables and row validity, all on the device
  *   yamoe_b200_ep_dispatch      hidden rows -> owner's recv buffer (peer stores)
  *   (any stream-ordered collective as a barrier)
- *   yamoe_b200_ep_local_forward gate_up + GLU + down on the received rows -> y_rows [max_rows, H]
- *   yamoe_b200_ep_return        y rows -> source rank's back buffer (peer stores; zeros if dropped)
+ *   yamoe_b200_ep_local_forward gate_up + GLU + down on the received rows.  With y_rows == NULL the
+ *                               down GEMM's epilogue stores every result row straight into the
+ *                               source rank's back buffer (GEMM and combine exchange in one
+ *                               kernel; needs peer_back given to ep_plan); otherwise it writes
+ *                               y_rows [max_rows, H] and
+ *   yamoe_b200_ep_return        sends them (peer stores; zeros if dropped)
  *   (barrier)                   then yamoe_b200_combine_rows on `back`
  * No host synchronisation and no host-side split sizes are involved.  The kernels only store
  * to peer memory; none of them reads from or waits on another GPU.
  * ------------------------------------------------------------------------------------------- */
 size_t yamoe_b200_ep_workspace_bytes(int64_t max_rows, int H, int E, int G, int dtype);
 int yamoe_b200_ep_plan(const int32_t *counts_all, int G, int rank, int E, int64_t expert_capacity,
-                       int64_t max_rows, int H, int dtype, void *workspace, size_t workspace_bytes, void *stream);
+                       void *const *peer_back, int64_t max_rows, int H, int dtype, void *workspace,
+                       size_t workspace_bytes, void *stream);
 int yamoe_b200_ep_dispatch(const void *hidden_states, const int32_t *sorted_values, const int32_t *sorted_indices,
                            const int32_t *bins, int64_t S, void *const *peer_recv, int64_t max_rows, int H, int E,
                            int G, int K, int dtype, const void *workspace, void *stream);

@@ -97,7 +97,7 @@ def test_permute_and_combine_rows_single_gpu():
         assert half.float().abs().sum() < out.float().abs().sum()
 
 
-def _peer_worker(rank, world, port, q):
+def _peer_worker(rank, world, port, q, fused=True):
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -107,7 +107,8 @@ def _peer_worker(rank, world, port, q):
         from yamoe_b200 import ep, workloads
         outs = []
         H, E, K = 256, 16, 4
-        ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=1024, max_tokens_local=512, dtype=torch.bfloat16)
+        ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=1024, max_tokens_local=512, dtype=torch.bfloat16,
+                                    fused_return=fused)
         # three calls in a row on the same buffers: full capacity, a dropping capacity, fewer tokens
         for T, cap, skew, seed in ((1024, 1024, False, 9), (1024, 100, True, 10), (512, 512, True, 11)):
             inp = workloads.make_inputs(T, H, E, K, seed=seed, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16,
@@ -127,8 +128,10 @@ def _peer_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_peer_store_ep_two_gpus():
-    """Dispatch and combine as peer stores with on-device offsets (no host round trip)."""
+@pytest.mark.parametrize("fused", [True, False])
+def test_peer_store_ep_two_gpus(fused):
+    """Dispatch and combine as peer stores with on-device offsets (no host round trip); with
+    `fused` the down GEMM's epilogue itself performs the combine stores."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -137,7 +140,7 @@ def test_peer_store_ep_two_gpus():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29800 + os.getpid() % 1000
-    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port + int(fused), q, fused)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(2)]

@@ -41,8 +41,8 @@ SIGNATURES = {
     "yamoe_b200_combine_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                                         c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_ep_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
-    "yamoe_b200_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t,
-                                   c_void_p]),
+    "yamoe_b200_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p,
+                                   c_size_t, c_void_p]),
     "yamoe_b200_ep_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int,
                                        c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "yamoe_b200_ep_local_forward": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),

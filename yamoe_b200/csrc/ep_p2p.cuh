@@ -30,6 +30,7 @@ struct EpTables {
   int32_t* dest_row;       // [E]      first row on the owner of expert e for rows sent by this rank
   int32_t* src_start;      // [G*per]  start of expert (r*per+le) in source s's sorted order
   int32_t* seg_row;        // [G*per]  first local row of the rows source s sent for local expert le
+  int64_t* row_dest;       // [max_rows] address of the row's slot in its source rank's back buffer, 0 for padding
 };
 
 // One CTA.  counts_all[s*E + e] = assignments of source rank s to global expert e.
@@ -110,20 +111,57 @@ ep_plan_kernel(const int32_t* __restrict__ counts_all, int G, int rank, int E, E
   }
 }
 
-// row_token[r] = r for kept rows, -1 for padding and for rows beyond the capacity; weight 1.
-__global__ void ep_rowtables_kernel(EpTables t, int64_t capacity, int64_t max_rows) {
+// row_token[r] = r for kept rows, -1 for padding and for rows beyond the capacity; weight 1;
+// row_dest[r] = where the row's result goes in the peer memory of the rank it came from.
+__global__ void ep_rowtables_kernel(EpTables t, int64_t capacity, int64_t max_rows, void* const* peer_back,
+                                    int G, int per, int64_t row_bytes) {
   const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= max_rows) return;
   int32_t tok = -1;
+  int64_t dest = 0;
   if (r < t.rt.header[kHdrRowsUsed]) {
     const int le = t.rt.tile_expert[r / kTileM];
     const int64_t i = r - t.rt.pad_off[le];
     const int64_t c = t.rt.counts[le];
     if (i < (c < capacity ? c : capacity)) tok = (int32_t)r;
+    if (i < c && peer_back != nullptr) {
+      int s = 0;
+      while (s + 1 < G && t.seg_row[(s + 1) * per + le] <= r) ++s;
+      const int64_t dst_row = (int64_t)t.src_start[s * per + le] + (r - t.seg_row[s * per + le]);
+      dest = reinterpret_cast<int64_t>(peer_back[s]) + dst_row * row_bytes;
+    }
   }
   t.rt.row_token[r] = tok;
   t.rt.row_weight[r] = 1.0f;
+  t.row_dest[r] = dest;
 }
+
+// Down-projection epilogue fused with the combine exchange: the bias-added result row goes
+// straight into the back buffer of the rank that owns the token (a peer store over NVLink);
+// rows dropped by the capacity send zeros, padding rows send nothing.
+template <typename T>
+struct EpiPeerRows {
+  const T* bias;             // [per, N]
+  const int64_t* row_dest;
+  const int32_t* row_token;
+  int N;
+
+  template <int NV>
+  __device__ __forceinline__ void apply(int e, int row, int n0, const float (&v)[NV]) const {
+    const int64_t dest = row_dest[row];
+    if (dest == 0) return;
+    float o[NV];
+    if (row_token[row] < 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] = 0.f;
+    } else {
+      load_vec<T, NV>(bias + (size_t)e * N + n0, o);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] += v[i];
+    }
+    store_vec<T, NV>(reinterpret_cast<T*>(dest) + n0, o);
+  }
+};
 
 // One warp per sorted assignment j: copies hidden[token] into the owner's recv_x.
 template <typename T>

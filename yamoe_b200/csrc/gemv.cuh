@@ -108,6 +108,7 @@ gemv_kernel(const GemvArgs g) {
   __shared__ int s_my_e, s_touched;
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  if constexpr (STAGE == kGateUp) pdl_trigger();   // stage two may set up its routing while this kernel streams
   if constexpr (STAGE == kGateUp) {
     // every CTA of the grid (also those that find no expert below) clears a share of the buffers
     // the second launch accumulates into; that launch starts only after this one has finished
@@ -170,6 +171,8 @@ gemv_kernel(const GemvArgs g) {
   }
   const int n_all = cnt[e];
   const int n_rows = (int64_t)n_all < g.capacity ? n_all : (int)g.capacity;
+  // everything above read only the caller's inputs; below come act / out32 / slab counters
+  if constexpr (STAGE == kDown) pdl_wait();
 
   const int n0 = blockIdx.y * NB;
   const int cg = lane % LPR;
@@ -292,7 +295,11 @@ inline int launch_gemv_stage(const GemvArgs& g, cudaStream_t st) {
   }
   const int slots = g.E < g.S ? g.E : g.S;
   dim3 grid((unsigned)slots, (unsigned)ceil_div(g.N, NB));
-  kern<<<grid, kGemvThreads, smem, st>>>(g);
+  if (STAGE == kDown) {
+    if (launch_pdl(kern, grid, dim3(kGemvThreads), smem, st, g) != cudaSuccess) return YAMOE_ERR_CUDA;
+  } else {
+    kern<<<grid, kGemvThreads, smem, st>>>(g);
+  }
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 

@@ -15,6 +15,8 @@ template <typename T>
 __global__ void __launch_bounds__(kRowWarps * 32)
 gather_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, const int32_t* __restrict__ row_token,
                    const int32_t* __restrict__ header, int H) {
+  pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   if (row >= header[kHdrRowsUsed]) return;
   const int lane = threadIdx.x & 31;
@@ -87,34 +89,57 @@ __global__ void cast_kernel(const float* __restrict__ acc, T* __restrict__ out, 
 // dst[e, n] = sum over the kept rows r of expert e of  w_r * src[r, n]   (WEIGHTED)
 //                                                  or       src[r, n]
 // reference: csrc/experts_backward.cu:277 (down bias), :308 (gate_up bias).  fp32 accumulation.
-// grid (ceil(N / 256), E); empty experts get exact zeros.
+// grid (ceil(N / (32 * elements per 16 bytes)), E); empty experts get exact zeros.
 template <typename T, bool WEIGHTED>
 __global__ void __launch_bounds__(256)
 colsum_kernel(const T* __restrict__ src, const float* __restrict__ row_weight,
               const int32_t* __restrict__ pad_off, const int32_t* __restrict__ counts, int64_t capacity,
               T* __restrict__ dst, int N) {
+  // 256 columns per CTA: a lane owns VE adjacent columns (one 16-byte load), the 8 warps take
+  // every 8th row, partial sums meet in shared memory.
+  constexpr int VE = 16 / (int)sizeof(T);
+  constexpr int CPB = 32 * VE;                 // columns per CTA
+  __shared__ float part[8][CPB];
   const int e = blockIdx.y;
-  const int n = blockIdx.x * 256 + threadIdx.x;
-  if (n >= N) return;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int n = blockIdx.x * CPB + lane * VE;
   const int r0 = pad_off[e];
   const int c = counts[e];
   const int kept = (int64_t)c < capacity ? c : (int)capacity;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  int r = 0;
-  for (; r + 4 <= kept; r += 4) {
-    const T* p = src + (size_t)(r0 + r) * N + n;
-    float v0 = DT<T>::ld(p), v1 = DT<T>::ld(p + N), v2 = DT<T>::ld(p + 2 * (size_t)N), v3 = DT<T>::ld(p + 3 * (size_t)N);
-    if constexpr (WEIGHTED) {
-      v0 *= row_weight[r0 + r]; v1 *= row_weight[r0 + r + 1]; v2 *= row_weight[r0 + r + 2]; v3 *= row_weight[r0 + r + 3];
+  float acc[VE];
+#pragma unroll
+  for (int j = 0; j < VE; ++j) acc[j] = 0.f;
+  if (n < N) {
+    int r = w;
+    for (; r + 24 < kept; r += 32) {           // four rows in flight per warp
+      float v[4][VE];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) load_vec<T, VE>(src + (size_t)(r0 + r + 8 * u) * N + n, v[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float wgt = WEIGHTED ? row_weight[r0 + r + 8 * u] : 1.0f;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) acc[j] = fmaf(wgt, v[u][j], acc[j]);
+      }
     }
-    s0 += v0; s1 += v1; s2 += v2; s3 += v3;
+    for (; r < kept; r += 8) {
+      float v[VE];
+      load_vec<T, VE>(src + (size_t)(r0 + r) * N + n, v);
+      const float wgt = WEIGHTED ? row_weight[r0 + r] : 1.0f;
+#pragma unroll
+      for (int j = 0; j < VE; ++j) acc[j] = fmaf(wgt, v[j], acc[j]);
+    }
   }
-  for (; r < kept; ++r) {
-    float v = DT<T>::ld(src + (size_t)(r0 + r) * N + n);
-    if constexpr (WEIGHTED) v *= row_weight[r0 + r];
-    s0 += v;
+#pragma unroll
+  for (int j = 0; j < VE; ++j) part[w][lane * VE + j] = acc[j];
+  __syncthreads();
+  for (int col = threadIdx.x; col < CPB; col += 256) {
+    if (blockIdx.x * CPB + col >= N) continue;
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += part[k][col];
+    DT<T>::st(dst + (size_t)e * N + blockIdx.x * CPB + col, s);
   }
-  DT<T>::st(dst + (size_t)e * N + n, (s0 + s1) + (s2 + s3));
 }
 
 // d_routing[t, e] (dense) or d_routing[t, slot] = gw_row[row] for every kept row.
@@ -139,6 +164,7 @@ template <typename T>
 __global__ void __launch_bounds__(kRowWarps * 32)
 combine_padded_kernel(const T* __restrict__ y, const int32_t* __restrict__ flat_row, T* __restrict__ out,
                       int64_t Tn, int H, int K) {
+  pdl_wait();
   const int64_t t = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   if (t >= Tn) return;
   const int lane = threadIdx.x & 31;

@@ -191,6 +191,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  // Set-up is done: let the next kernel on the stream begin its own set-up, then wait until the
+  // previous kernel has completed before touching anything it produced.
+  pdl_trigger();
+  pdl_wait();
 
   // ---- tile walk (identical in every role) ---------------------------------------------------
   const int NT = (p.N + BN - 1) / BN;
@@ -481,7 +485,8 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
   int64_t total_max = MODE == kWgrad ? (int64_t)g.E * ceil_div(g.M, kUmmaBM) * NT : max_tiles * NT;
   int grid = (int)std::min<int64_t>(total_max, umma_sm_count());
   if (grid <= 0) return YAMOE_OK;
-  kern<<<grid, kUmmaThreads, SM::kTotal, stream>>>(tmA, tmB, p, epi);
+  if (launch_pdl(kern, dim3(grid), dim3(kUmmaThreads), SM::kTotal, stream, tmA, tmB, p, epi) != cudaSuccess)
+    return YAMOE_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 

@@ -182,9 +182,10 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
   const unsigned row_blocks = (unsigned)ceil_div(p.max_rows, kRowWarps);
   {
     StageTimer tm(kStageGather, st);
-    gather_rows_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const T*>(hidden),
-                                                                reinterpret_cast<T*>(p.xs), p.rt.row_token,
-                                                                p.rt.header, H);
+    if (launch_pdl(gather_rows_kernel<T>, dim3(row_blocks), dim3(kRowWarps * 32), 0, st,
+                   reinterpret_cast<const T*>(hidden), reinterpret_cast<T*>(p.xs),
+                   (const int32_t*)p.rt.row_token, (const int32_t*)p.rt.header, H) != cudaSuccess)
+      return YAMOE_ERR_CUDA;
   }
   EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), reinterpret_cast<T*>(p.act), nullptr, nullptr,
                 p.rt.row_token, p.rt.row_weight, H};
@@ -209,8 +210,10 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
         rc = launch_umma<kFwd>(g2, wrows, p.max_rows, p.max_tiles, st);
       }
       if (rc) return rc;
-      combine_padded_kernel<T><<<(unsigned)ceil_div(Tn, kRowWarps), kRowWarps * 32, 0, st>>>(
-          reinterpret_cast<const T*>(p.yrows), p.rt.flat_row, reinterpret_cast<T*>(out), Tn, H, K);
+      if (launch_pdl(combine_padded_kernel<T>, dim3((unsigned)ceil_div(Tn, kRowWarps)), dim3(kRowWarps * 32), 0, st,
+                     reinterpret_cast<const T*>(p.yrows), (const int32_t*)p.rt.flat_row, reinterpret_cast<T*>(out),
+                     Tn, H, K) != cudaSuccess)
+        return YAMOE_ERR_CUDA;
       return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
     }
   } else {
@@ -303,10 +306,10 @@ static int backward_impl(const void* grad_out, int per_slot, const void* hidden,
     launch_simt_gemm<T, kWgrad>(g5, st_wgu, p.max_rows, st);
   }
   // bias gradients and routing-weight gradients
-  colsum_kernel<T, true><<<dim3((unsigned)ceil_div(H, 256), E), 256, 0, st>>>(
+  colsum_kernel<T, true><<<dim3((unsigned)ceil_div(H, 512 / (int)sizeof(T)), E), 256, 0, st>>>(
       reinterpret_cast<const T*>(p.gys), p.rt.row_weight, p.rt.pad_off, p.rt.counts, cap,
       reinterpret_cast<T*>(d_bd), H);
-  colsum_kernel<T, false><<<dim3((unsigned)ceil_div(2 * H, 256), E), 256, 0, st>>>(
+  colsum_kernel<T, false><<<dim3((unsigned)ceil_div(2 * H, 512 / (int)sizeof(T)), E), 256, 0, st>>>(
       reinterpret_cast<const T*>(p.gpre), p.rt.row_weight, p.rt.pad_off, p.rt.counts, cap,
       reinterpret_cast<T*>(d_bgu), 2 * H);
   routing_grad_kernel<T><<<(unsigned)ceil_div(p.max_rows, 256), 256, 0, st>>>(
@@ -399,6 +402,7 @@ static EpPlan plan_ep(void* ws, int64_t max_rows, int H, int E, int G, int dtype
   p.t.dest_row = b.take<int32_t>(E);
   p.t.src_start = b.take<int32_t>((size_t)G * per);
   p.t.seg_row = b.take<int32_t>((size_t)G * per);
+  p.t.row_dest = b.take<int64_t>(max_rows);
   p.act = b.take<char>((size_t)max_rows * H * (dtype == YAMOE_BF16 ? 2 : 4));
   p.bytes = b.off + 256;
   return p;
@@ -421,6 +425,8 @@ static int ep_local_forward_impl(const void* recv_x, const void* wgu, const void
                 rt.row_weight, H};
   EpiWeightedRows<T> wrows{reinterpret_cast<const T*>(bd), reinterpret_cast<T*>(yrows), rt.row_token,
                            rt.row_weight, H};
+  EpiPeerRows<T> prows{reinterpret_cast<const T*>(bd), p.t.row_dest, rt.row_token, H};
+  const bool fused = yrows == nullptr;     // results go straight to the source ranks
   GemmArgs g1{recv_x, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, per, rt.tile_expert, rt.pad_off,
               rt.header};
   g1.pair_expert = rt.pair_expert; g1.pair_off = rt.pair_off;
@@ -435,12 +441,14 @@ static int ep_local_forward_impl(const void* recv_x, const void* wgu, const void
       }
       if (rc) return rc;
       StageTimer tm(kStageDown, st);
-      rc = launch_umma<kFwd>(g2, wrows, max_rows, max_tiles, st);
+      rc = fused ? launch_umma<kFwd>(g2, prows, max_rows, max_tiles, st)
+                 : launch_umma<kFwd>(g2, wrows, max_rows, max_tiles, st);
       if (rc) return rc;
     }
   } else {
     launch_simt_gemm<T, kFwd>(g1, glu, max_rows, st);
-    launch_simt_gemm<T, kFwd>(g2, wrows, max_rows, st);
+    if (fused) launch_simt_gemm<T, kFwd>(g2, prows, max_rows, st);
+    else launch_simt_gemm<T, kFwd>(g2, wrows, max_rows, st);
   }
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
@@ -729,7 +737,8 @@ size_t yamoe_b200_ep_workspace_bytes(int64_t max_rows, int H, int E, int G, int 
 }
 
 int yamoe_b200_ep_plan(const int32_t* counts_all, int G, int rank, int E, int64_t expert_capacity,
-                       int64_t max_rows, int H, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+                       void* const* peer_back, int64_t max_rows, int H, int dtype, void* workspace,
+                       size_t workspace_bytes, void* stream) {
   int rc = check_ep(max_rows, H, E, G, rank, dtype);
   if (rc) return rc;
   if (!counts_all || expert_capacity < 0) return YAMOE_ERR_BAD_ARG;
@@ -740,7 +749,8 @@ int yamoe_b200_ep_plan(const int32_t* counts_all, int G, int rank, int E, int64_
   EpPlan p = plan_ep(workspace, max_rows, H, E, G, dtype);
   YB_CUDA_OK(cudaMemsetAsync(p.t.rt.header, 0, 16 * sizeof(int32_t), st));
   ep_plan_kernel<<<1, 256, (size_t)3 * E * sizeof(int32_t), st>>>(counts_all, G, rank, E, p.t);
-  ep_rowtables_kernel<<<(unsigned)ceil_div(max_rows, 256), 256, 0, st>>>(p.t, expert_capacity, max_rows);
+  ep_rowtables_kernel<<<(unsigned)ceil_div(max_rows, 256), 256, 0, st>>>(
+      p.t, expert_capacity, max_rows, peer_back, G, E / G, (int64_t)H * (dtype == YAMOE_BF16 ? 2 : 4));
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
@@ -771,7 +781,7 @@ int yamoe_b200_ep_local_forward(const void* recv_x, const void* gate_up_proj, co
                                 int H, int E, int G, int dtype, void* workspace, void* stream) {
   int rc = check_ep(max_rows, H, E, G, 0, dtype);
   if (rc) return rc;
-  if (!recv_x || !gate_up_proj || !gate_up_proj_bias || !down_proj || !down_proj_bias || !y_rows || !workspace)
+  if (!recv_x || !gate_up_proj || !gate_up_proj_bias || !down_proj || !down_proj_bias || !workspace)
     return YAMOE_ERR_BAD_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   EpPlan p = plan_ep(workspace, max_rows, H, E, G, dtype);

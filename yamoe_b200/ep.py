@@ -182,13 +182,16 @@ class PeerExpertParallel:
     assignment lands on one rank) and `max_tokens_local` tokens on this rank.
 
     Sequence per call (one stream): route -> all_gather(counts) -> plan -> dispatch (peer stores) ->
-    barrier -> grouped GEMMs on the received rows -> return (peer stores) -> barrier -> combine.
+    barrier -> grouped GEMMs on the received rows, the down GEMM's epilogue storing each result row
+    straight into the token owner's buffer (`fused_return`; otherwise a separate return kernel) ->
+    barrier -> combine.
     The barriers are stream-ordered collectives; no kernel of this path waits on another GPU.
     """
 
     def __init__(self, hidden: int, num_experts: int, top_k: int, max_tokens_total: int, max_tokens_local: int,
-                 dtype=torch.bfloat16, group=None):
+                 dtype=torch.bfloat16, group=None, fused_return: bool = True):
         import torch.distributed._symmetric_memory as symm_mem
+        self.fused_return = bool(fused_return)
         from . import _lib
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
@@ -232,18 +235,21 @@ class PeerExpertParallel:
         sv, si, bins, counts = ops.route(router_indices, self.E)
         dist.all_gather_into_tensor(self.counts_all.view(-1), counts, group=self.group)
         self._check(L.yamoe_b200_ep_plan(self.counts_all.data_ptr(), self.world, self.rank, self.E,
-                                         int(expert_capacity), self.max_rows, self.H, self.dt, self.ws.data_ptr(),
-                                         self.ws.numel(), st), "ep_plan")
+                                         int(expert_capacity), self.peer_back.data_ptr(), self.max_rows, self.H,
+                                         self.dt, self.ws.data_ptr(), self.ws.numel(), st), "ep_plan")
         self._check(L.yamoe_b200_ep_dispatch(hs.data_ptr(), sv.data_ptr(), si.data_ptr(), bins.data_ptr(), T * K,
                                              self.peer_recv.data_ptr(), self.max_rows, self.H, self.E, self.world, K,
                                              self.dt, self.ws.data_ptr(), st), "ep_dispatch")
         self._barrier()
+        y_ptr = None if self.fused_return else self.y_rows.data_ptr()
         self._check(L.yamoe_b200_ep_local_forward(self.recv.data_ptr(), gate_up_local.data_ptr(),
                                                   gate_up_bias_local.data_ptr(), down_local.data_ptr(),
-                                                  down_bias_local.data_ptr(), self.y_rows.data_ptr(), self.max_rows,
+                                                  down_bias_local.data_ptr(), y_ptr, self.max_rows,
                                                   self.H, self.E, self.world, self.dt, self.ws.data_ptr(), st),
                     "ep_local_forward")
-        self._check(L.yamoe_b200_ep_return(self.y_rows.data_ptr(), self.peer_back.data_ptr(), self.max_rows, self.H,
-                                           self.E, self.world, self.dt, self.ws.data_ptr(), st), "ep_return")
+        if not self.fused_return:
+            self._check(L.yamoe_b200_ep_return(self.y_rows.data_ptr(), self.peer_back.data_ptr(), self.max_rows,
+                                               self.H, self.E, self.world, self.dt, self.ws.data_ptr(), st),
+                        "ep_return")
         self._barrier()
         return ops.combine_rows(self.back[: T * K], si, router_indices, routing_weights, self.E)
