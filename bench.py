@@ -234,8 +234,9 @@ def run_ours(args):
         T = hi - lo
         ep_stats = {}
         peer_ctx = None
-        if args.ep_mode == "peer" and w["mode"] == "fwd":
-            peer_ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=T_total, max_tokens_local=T, dtype=dtype)
+        if args.ep_mode in ("peer", "peer-fused") and w["mode"] == "fwd":
+            peer_ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=T_total, max_tokens_local=T, dtype=dtype,
+                                             fused_return=(args.ep_mode == "peer-fused"))
 
     def step():
         if use_ep and w["mode"] == "bwd":
@@ -346,7 +347,7 @@ def run_ours(args):
             "config": {"workload": args.workload, "tokens": T, "hidden": H, "experts": E, "top_k": K,
                        "pass": w["mode"], "expert_capacity": cap,
                        "parallelism": (f"ep{world} (tokens sharded by rows, experts sharded contiguously, "
-                                       + ("dispatch + combine as NVLink peer stores, offsets on device, no host sync)"
+                                       + (f"dispatch + combine as NVLink peer stores [{args.ep_mode}], offsets on device, no host sync)"
                                           if use_ep and peer_ctx is not None else
                                           "NCCL all-to-all dispatch + combine; rank-0 rows sent/received "
                                           f"{ep_stats.get('rows_sent')}/{ep_stats.get('rows_received')})")) if use_ep else
@@ -393,7 +394,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gptoss20b_fwd_t4096", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ep-mode", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--ep-mode", default="peer", choices=["peer", "peer-fused", "nccl"],
                     help="exchange used by the expert-parallel workloads on N > 1 GPUs")
     ap.add_argument("--traffic", type=float, default=1.268e9,
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (see profiles/)")

@@ -189,7 +189,7 @@ class PeerExpertParallel:
     """
 
     def __init__(self, hidden: int, num_experts: int, top_k: int, max_tokens_total: int, max_tokens_local: int,
-                 dtype=torch.bfloat16, group=None, fused_return: bool = True):
+                 dtype=torch.bfloat16, group=None, fused_return: bool = False):
         import torch.distributed._symmetric_memory as symm_mem
         self.fused_return = bool(fused_return)
         from . import _lib
