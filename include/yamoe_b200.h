@@ -218,6 +218,16 @@ int yamoe_b200_ep_local_forward(const void *recv_x, const void *gate_up_proj, co
 int yamoe_b200_ep_return(const void *y_rows, void *const *peer_back, int64_t max_rows, int H, int E, int G,
                          int dtype, const void *workspace, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Router tail of the layer that calls the expert op.  Replaces the top-k / softmax / scatter
+ * chain of Yamoe.forward (torch-ext/yamoe/layers.py:136-149):
+ *   router_indices [T,K] int64  = experts of the K largest logits, descending
+ *   router_scores  [T,E] dtype  = softmax over those K logits at the selected columns, 0 elsewhere
+ * E <= 1024, K <= 32.  Ties between equal logits go to the lower expert id.
+ * ------------------------------------------------------------------------------------------- */
+int yamoe_b200_router_topk(const void *router_logits, int64_t *router_indices, void *router_scores, int64_t T,
+                           int E, int K, int dtype, void *stream);
+
 /* Device status word of the last forward/backward call that used `workspace`: 0 when every
  * bounded device-side wait completed, otherwise a code naming the wait that gave up.  Reads
  * 4 bytes from the device with cudaMemcpyAsync on `stream` and synchronises that stream. */

@@ -162,6 +162,16 @@ def experts_backward_oracle(grad_out, hidden_states, router_indices, routing_wei
 from yamoe_b200.workloads import make_inputs, make_readme_inputs, make_routing  # noqa: E402,F401
 
 
+def router_oracle(hidden, router_weight, router_bias, top_k):
+    """Router of the layer that feeds the expert op (torch-ext/yamoe/vendored/gpt_oss_mlp.py:127-139,
+    torch-ext/yamoe/layers.py:126-149): logits = x W^T + b, top-k on the logits, softmax over the k
+    selected logits, dense [T,E] scores.  Returns (router_scores, router_indices)."""
+    logits = torch.nn.functional.linear(hidden, router_weight, router_bias)
+    top_v, idx = torch.topk(logits, top_k, dim=-1)
+    top_w = torch.softmax(top_v, dim=-1)
+    return torch.zeros_like(logits).scatter_(1, idx, top_w), idx
+
+
 def check_close(x, ref, rtol, name="", rel_l2=None):
     """|x - ref| <= rtol*|ref| + rtol*max|ref| elementwise (and optionally a rel-L2 bound).
     Returns (max_violation_ratio, rel_l2) and raises AssertionError on failure."""

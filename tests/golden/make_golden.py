@@ -110,6 +110,29 @@ def main():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **save)
         print(name, "ok", out_train.abs().max().item())
 
+    # whole layer (router + experts) from the vendored GptOssMLP
+    T, H, E, K = 48, 32, 8, 2
+    cfg = types.SimpleNamespace(intermediate_size=H, num_local_experts=E, hidden_size=H, num_experts_per_tok=K)
+    gen = torch.Generator().manual_seed(7)
+    mlp = twin.GptOssMLP(cfg)
+    with torch.no_grad():
+        for prm, std in ((mlp.router.weight, 0.5), (mlp.router.bias, 0.5), (mlp.experts.gate_up_proj, 0.35),
+                         (mlp.experts.gate_up_proj_bias, 0.5), (mlp.experts.down_proj, 0.35),
+                         (mlp.experts.down_proj_bias, 0.5)):
+            prm.copy_(torch.randn(prm.shape, generator=gen) * std)
+    x = torch.randn(2, T // 2, H, generator=gen)
+    mlp.train(False)
+    with torch.no_grad():
+        out_mlp, scores = mlp(x)
+    np.savez_compressed(os.path.join(HERE, "mlp_small.npz"), x=x.numpy(), out=out_mlp.numpy(), scores=scores.numpy(),
+                        router_weight=mlp.router.weight.detach().numpy(), router_bias=mlp.router.bias.detach().numpy(),
+                        gate_up_proj=mlp.experts.gate_up_proj.detach().numpy(),
+                        gate_up_proj_bias=mlp.experts.gate_up_proj_bias.detach().numpy(),
+                        down_proj=mlp.experts.down_proj.detach().numpy(),
+                        down_proj_bias=mlp.experts.down_proj_bias.detach().numpy(),
+                        dims=np.array([T, H, E, K], dtype=np.int64))
+    print("mlp_small ok", out_mlp.abs().max().item())
+
     # README workload digest (full size, fp32, forward only)
     inp = orc.make_readme_inputs(batch=2)
     T, H, E, K = 512, 2880, 8, 2

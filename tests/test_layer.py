@@ -1,0 +1,106 @@
+"""The layer front-end (router + experts): oracle against the golden vectors of the reference's
+GptOssMLP on CPU; the CUDA `Yamoe` module and the fused router kernel on GPU."""
+import types
+
+import pytest
+import torch
+
+from oracle import experts_oracle as orc
+from helpers import load_golden
+
+
+def _golden_layer():
+    g = load_golden("mlp_small")
+    T, H, E, K = g["dims"].tolist()
+    return g, T, H, E, K
+
+
+def test_router_and_layer_oracle_match_reference_mlp():
+    g, T, H, E, K = _golden_layer()
+    x = g["x"].reshape(T, H)
+    scores, idx = orc.router_oracle(x, g["router_weight"], g["router_bias"], K)
+    orc.check_close(scores, g["scores"], 1e-5, "router scores")
+    out = orc.experts_forward_oracle(x, idx, scores, g["gate_up_proj"], g["gate_up_proj_bias"], g["down_proj"],
+                                     g["down_proj_bias"], T, E, K)
+    orc.check_close(out, g["out"].reshape(T, H), 1e-5, "layer output")
+
+
+def _module(g, E, K, dtype=torch.float32, capacity=None):
+    import yamoe_b200
+    m = yamoe_b200.Yamoe()
+    m.router = types.SimpleNamespace(weight=g["router_weight"].to(dtype).cuda(), bias=g["router_bias"].to(dtype).cuda())
+    m.experts = types.SimpleNamespace(**{k: g[k].to(dtype).cuda() for k in
+                                         ["gate_up_proj", "gate_up_proj_bias", "down_proj", "down_proj_bias"]})
+    m.num_experts, m.top_k = E, K
+    if capacity is not None:
+        m.expert_capacity = capacity
+    return m
+
+
+@pytest.mark.gpu
+def test_router_topk_kernel():
+    import yamoe_b200
+    for T, E, K, dtype in ((48, 8, 2, torch.float32), (1000, 32, 4, torch.float32), (257, 128, 4, torch.bfloat16),
+                           (5, 1024, 8, torch.float32), (3, 5, 5, torch.float32)):
+        logits = torch.randn(T, E, generator=torch.Generator().manual_seed(T)).to(dtype)
+        idx, scores = yamoe_b200.router_topk(logits.cuda(), K)
+        top_v, ref_idx = torch.topk(logits.float(), K, dim=-1)
+        ref_scores = torch.zeros(T, E).scatter_(1, ref_idx, torch.softmax(top_v, -1))
+        if dtype == torch.float32:
+            assert torch.equal(idx.cpu(), ref_idx)
+        else:   # bf16 logits can tie; compare the selected values instead of the ids
+            assert torch.equal(torch.gather(logits.float(), 1, idx.cpu()), top_v)
+        tol = 1e-6 if dtype == torch.float32 else 1e-2
+        # compare the K score values per row (ids may differ where bf16 logits tie)
+        got_sorted = scores.float().cpu().sort(dim=1, descending=True).values[:, :K]
+        ref_sorted = ref_scores.sort(dim=1, descending=True).values[:, :K]
+        assert (got_sorted - ref_sorted).abs().max() <= tol
+        assert (torch.gather(scores.float().cpu(), 1, idx.cpu()) > 0).all()
+        assert int((scores != 0).sum(1).max()) <= K
+
+
+@pytest.mark.gpu
+def test_yamoe_module_matches_reference_mlp():
+    g, T, H, E, K = _golden_layer()
+    m = _module(g, E, K, capacity=T)
+    with torch.no_grad():
+        out, scores = m(g["x"].cuda())
+    orc.check_close(scores.cpu(), g["scores"], 1e-5, "router scores")
+    orc.check_close(out.cpu(), g["out"], 1e-4, "layer output vs GptOssMLP")
+
+
+@pytest.mark.gpu
+def test_yamoe_module_default_capacity_and_grads():
+    g, T, H, E, K = _golden_layer()
+    x = g["x"].reshape(T, H)
+    scores, idx = orc.router_oracle(x, g["router_weight"], g["router_bias"], K)
+    cap = -(-T * K // E)                                   # reference formula, layers.py:162
+    ref = orc.experts_forward_oracle(x, idx, scores, g["gate_up_proj"], g["gate_up_proj_bias"], g["down_proj"],
+                                     g["down_proj_bias"], cap, E, K)
+    m = _module(g, E, K)
+    with torch.no_grad():
+        out, _ = m(g["x"].cuda())
+    orc.check_close(out.cpu().reshape(T, H), ref, 1e-4, "default capacity (drops)")
+    # with autograd recording, gradients reach the input, the router and the experts
+    m = _module(g, E, K, capacity=T)
+    for t in (m.router.weight, m.router.bias, m.experts.gate_up_proj, m.experts.down_proj):
+        t.requires_grad_(True)
+    xin = g["x"].cuda().requires_grad_(True)
+    out, _ = m(xin)
+    out.square().sum().backward()
+    # reference gradients by autograd through the oracle on CPU
+    xr = g["x"].clone().requires_grad_(True)
+    rw_, rb_ = g["router_weight"].clone().requires_grad_(True), g["router_bias"].clone().requires_grad_(True)
+    sc, ix = orc.router_oracle(xr.reshape(T, H), rw_, rb_, K)
+    wgu = g["gate_up_proj"].clone().requires_grad_(True)
+    o = torch.zeros(T, H)
+    sel = torch.gather(sc, 1, ix)
+    for k in range(K):
+        e = ix[:, k]
+        pre = torch.einsum("th,thn->tn", xr.reshape(T, H), wgu[e]) + g["gate_up_proj_bias"][e]
+        y = torch.einsum("th,thn->tn", orc.glu(pre), g["down_proj"][e]) + g["down_proj_bias"][e]
+        o = o + sel[:, k:k + 1] * y
+    o.square().sum().backward()
+    orc.check_close(xin.grad.cpu(), xr.grad, 1e-3, "d input")
+    orc.check_close(m.router.weight.grad.cpu(), rw_.grad, 1e-3, "d router weight")
+    orc.check_close(m.experts.gate_up_proj.grad.cpu(), wgu.grad, 1e-3, "d gate_up_proj")

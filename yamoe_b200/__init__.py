@@ -1,8 +1,8 @@
 """yamoe_b200: the expert forward/backward op of drbh/yamoe as hand-written sm_100a CUDA behind
 the reference's operator interface (torch-ext/yamoe/__init__.py:6-12)."""
 from . import _lib
-from .layers import _ExpertsFn, experts_autograd
-from .ops import batch_mm, batch_mm_wgrad, bincount_cumsum, experts, experts_backward, route, sort
+from .layers import Yamoe, _ExpertsFn, experts_autograd
+from .ops import router_topk, batch_mm, batch_mm_wgrad, bincount_cumsum, experts, experts_backward, route, sort
 
 
 def set_path(name: str) -> str:
@@ -12,5 +12,5 @@ def set_path(name: str) -> str:
     return names[prev]
 
 
-__all__ = ["experts", "experts_backward", "sort", "bincount_cumsum", "route", "batch_mm", "batch_mm_wgrad", "experts_autograd",
+__all__ = ["experts", "experts_backward", "sort", "bincount_cumsum", "route", "batch_mm", "batch_mm_wgrad", "experts_autograd", "Yamoe", "router_topk",
            "_ExpertsFn", "set_path"]

@@ -47,6 +47,7 @@ SIGNATURES = {
                                        c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "yamoe_b200_ep_local_forward": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "yamoe_b200_ep_return": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "yamoe_b200_router_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "yamoe_b200_device_status": (c_int, [c_void_p, c_void_p, ctypes.POINTER(ctypes.c_int32)]),
 }
 

@@ -17,6 +17,7 @@
 #include "umma_gemm_2cta.cuh"
 #include "gemv.cuh"
 #include "ep_p2p.cuh"
+#include "router.cuh"
 
 namespace yb {
 
@@ -807,6 +808,17 @@ int yamoe_b200_ep_return(const void* y_rows, void* const* peer_back, int64_t max
     ep_return_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const float*>(y_rows), p.t,
                                                               peer_back, H, G, E / G);
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+int yamoe_b200_router_topk(const void* router_logits, int64_t* router_indices, void* router_scores, int64_t T, int E,
+                           int K, int dtype, void* stream) {
+  if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
+  if (T < 0 || E <= 0 || K <= 0 || K > E || K > kRouterMaxK || E > 32 * kRouterMaxPerLane) return YAMOE_ERR_BAD_ARG;
+  if (T == 0) return YAMOE_OK;
+  if (!router_logits || !router_indices || !router_scores) return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == YAMOE_BF16) return launch_router_topk<__nv_bfloat16>(router_logits, router_indices, router_scores, T, E, K, st);
+  return launch_router_topk<float>(router_logits, router_indices, router_scores, T, E, K, st);
 }
 
 int yamoe_b200_device_status(const void* workspace, void* stream, int32_t* status_out) {

@@ -34,3 +34,54 @@ def experts_autograd(hidden_flat, router_indices, routing_weights, gate_up_proj,
     """Differentiable `experts`: forward through the CUDA op, backward through `experts_backward`."""
     return _ExpertsFn.apply(hidden_flat, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias,
                             down_proj, down_proj_bias, expert_capacity, num_experts, top_k, enable_router_grads)
+
+
+def ceil_div(a, b):
+    return (a + b - 1) // b
+
+
+class Yamoe(torch.nn.Module):
+    """Drop-in `forward` for a GPT-OSS MoE block (an object with `router.weight`, `router.bias`,
+    `experts.gate_up_proj`, `experts.gate_up_proj_bias`, `experts.down_proj`,
+    `experts.down_proj_bias`, and optionally `num_experts`, `top_k`), returning
+    `(output [B,S,H], router_scores [T,E])` like the reference layer
+    (torch-ext/yamoe/layers.py:103-218; oracle torch-ext/yamoe/vendored/gpt_oss_mlp.py:142-159).
+
+    Differences from the reference layer, on purpose:
+    * `expert_capacity` defaults to the reference's `ceil(T*K/E)` (layers.py:162), which drops
+      assignments of over-subscribed experts; set the attribute `expert_capacity` (for example to
+      the token count) for a run that never drops and therefore matches `GptOssMLP`.
+    * gradients are not switched off: when autograd is recording, the router runs in PyTorch and
+      the experts go through `_ExpertsFn`, so router and expert weights receive gradients.  Without
+      autograd the top-k / softmax / scatter run in one CUDA kernel.
+    """
+    can_torch_compile: bool = False
+
+    def forward(self, hidden_states: torch.Tensor):
+        batch, seq, hidden = hidden_states.shape
+        T = batch * seq
+        E = getattr(self, "num_experts", self.router.weight.shape[0])
+        K = getattr(self, "top_k", 4)
+        x = hidden_states.reshape(T, hidden)
+        logits = torch.nn.functional.linear(x, self.router.weight, self.router.bias)
+        needs_grad = torch.is_grad_enabled() and (
+            x.requires_grad or self.router.weight.requires_grad or self.experts.gate_up_proj.requires_grad)
+        if needs_grad:
+            top_v, router_indices = torch.topk(logits, K, dim=-1)
+            top_w = torch.nn.functional.softmax(top_v, dim=-1, dtype=top_v.dtype)
+            router_scores = torch.zeros_like(logits).scatter(1, router_indices, top_w)
+        else:
+            router_indices, router_scores = ops.router_topk(logits, K)
+        cap = getattr(self, "expert_capacity", None)
+        if cap is None:
+            cap = ceil_div(T * K, E)
+        gate_up = self.experts.gate_up_proj[:, :, : 2 * hidden]
+        gate_up_bias = self.experts.gate_up_proj_bias[:, : 2 * hidden]
+        down = self.experts.down_proj[:, :hidden, :]
+        down_bias = self.experts.down_proj_bias
+        if needs_grad:
+            out = _ExpertsFn.apply(x, router_indices, router_scores, gate_up, gate_up_bias, down, down_bias,
+                                   int(cap), E, K, True)
+        else:
+            out = ops.experts(x, router_indices, router_scores, gate_up, gate_up_bias, down, down_bias, int(cap), E, K)
+        return out.view(batch, seq, hidden), router_scores

@@ -226,6 +226,22 @@ def combine_rows(rows: torch.Tensor, sorted_indices: torch.Tensor, router_indice
     return out
 
 
+def router_topk(router_logits: torch.Tensor, top_k: int):
+    """(router_indices [T,K] int64, router_scores [T,E]) from router logits [T,E]: top-k, softmax
+    over the k selected logits, dense scatter, in one kernel (torch-ext/yamoe/layers.py:136-149)."""
+    _require(router_logits.is_cuda and router_logits.dim() == 2 and router_logits.dtype in _DT,
+             "router_topk: 2D CUDA float32/bfloat16 logits expected")
+    logits = router_logits.contiguous()
+    T, E = logits.shape
+    idx = torch.empty(T, int(top_k), dtype=torch.int64, device=logits.device)
+    scores = torch.empty_like(logits)
+    with torch.cuda.device(logits.device):
+        st = _lib.lib().yamoe_b200_router_topk(logits.data_ptr(), idx.data_ptr(), scores.data_ptr(), T, E, int(top_k),
+                                               _DT[logits.dtype], _stream())
+        _lib.check(st, "router_topk")
+    return idx, scores
+
+
 experts = torch.ops.yamoe_b200.experts
 batch_mm = torch.ops.yamoe_b200.batch_mm
 experts_backward = torch.ops.yamoe_b200.experts_backward
