@@ -16,7 +16,6 @@
 #include "umma_gemm.cuh"
 #include "umma_gemm_2cta.cuh"
 #include "gemv.cuh"
-#include "gemv_splitk.cuh"
 #include "ep_p2p.cuh"
 #include "router.cuh"
 
@@ -62,7 +61,6 @@ struct Plan {
   void* yrows = nullptr;   // [max_rows, H]   weighted down-projection rows (bf16 two-step combine)
   float* acc32 = nullptr;  // [T, H]          fp32 combine target when the output is bf16
   int32_t* slab_done = nullptr;  // [ceil(H/64)] completion counters of the decode path
-  float* pre32 = nullptr;        // [min(S,256), 2H] fp32 pre-activations of the split-K decode path
   // backward
   void* gys = nullptr;     // [max_rows, H]   gathered grad_y rows
   void* pre = nullptr;     // [max_rows, 2H]  biased pre-activations
@@ -117,7 +115,6 @@ static Plan plan_forward(void* ws, int64_t T, int H, int E, int K, int dtype) {
     p.yrows = region;
   }
   p.slab_done = b.take<int32_t>((size_t)ceil_div(H, 64));
-  if (dtype == YAMOE_BF16 && p.S <= kGemvMaxS) p.pre32 = b.take<float>((size_t)p.S * 2 * H);
   p.bytes = b.off + 256;
   return p;
 }
@@ -169,12 +166,8 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
   if (Tn == 0) return YAMOE_OK;
 
   if (dtype == YAMOE_BF16 && (path == YAMOE_PATH_GEMV || (path == YAMOE_PATH_AUTO && gemv_preferred(Tn, E, K)))) {
-    int rc = YAMOE_ERR_UNSUPPORTED;
-    if (gemv_splitk_selected() && p.pre32 != nullptr)
-      rc = launch_gemv_splitk_forward(hidden, ridx, rw, rcols, wgu, bgu, wd, bd, out, Tn, H, E, K, cap, p.pre32, acc, st);
-    if (rc == YAMOE_ERR_UNSUPPORTED)
-      rc = launch_gemv_forward(hidden, ridx, rw, rcols, wgu, bgu, wd, bd, out, Tn, H, E, K, cap, p.act, acc,
-                               p.slab_done, st);
+    int rc = launch_gemv_forward(hidden, ridx, rw, rcols, wgu, bgu, wd, bd, out, Tn, H, E, K, cap, p.act, acc,
+                                 p.slab_done, st);
     if (rc != YAMOE_ERR_UNSUPPORTED) return rc;
   }
   const bool tc = use_tcgen05(path, dtype, H);
