@@ -318,27 +318,62 @@ def run_ours(args):
     h2d = sum(x.numel() * x.element_size() for x in host_in) + (host_go.numel() * host_go.element_size() if host_go is not None else 0)
     d2h = host_out.numel() * host_out.element_size()
 
-    def e2e_step():
-        a = [x.to("cuda", non_blocking=True) for x in host_in]
+    # Three streams pipeline consecutive steps: while step i computes, step i+1's inputs come in and
+    # step i-1's result goes out (PCIe is full duplex).  Every step still copies its own inputs from
+    # pinned host memory and its own result back; expert-parallel steps stay on one stream because
+    # their collectives must be issued in the same order on every rank.
+    pipelined = not use_ep
+    cur = torch.cuda.current_stream()
+    s_in, s_out = (torch.cuda.Stream(), torch.cuda.Stream()) if pipelined else (cur, cur)
+    host_outs = [host_out, torch.empty_like(host_out).pin_memory()]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    comp_done = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+    keep = [None, None]
+    dev_in = [[torch.empty_like(x, device="cuda") for x in host_in] for _ in range(2)]
+    dev_go = [torch.empty_like(host_go, device="cuda") if host_go is not None else None for _ in range(2)]
+
+    def run_op(a, g):
         if w["mode"] == "bwd":
-            g = host_go.to("cuda", non_blocking=True)
             outs = (ep.ep_experts_backward(g, *a, *dev[3:], cap, E, K) if use_ep
                     else yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K))
-            host_out.copy_(outs[0], non_blocking=True)
-        elif use_ep:
-            out = peer_ctx.forward(*a, *dev[3:], cap) if peer_ctx is not None else ep.ep_experts(*a, *dev[3:], cap, E, K)
-            host_out.copy_(out, non_blocking=True)
-        else:
-            out = yamoe_b200.experts(*a, *dev[3:], cap, E, K)
-            host_out.copy_(out, non_blocking=True)
+            return outs[0]
+        if use_ep:
+            return peer_ctx.forward(*a, *dev[3:], cap) if peer_ctx is not None else ep.ep_experts(*a, *dev[3:], cap, E, K)
+        return yamoe_b200.experts(*a, *dev[3:], cap, E, K)
 
-    for _ in range(min(args.warmup, 3)):
-        e2e_step()
+    def e2e_step(i):
+        b = i % 2
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(comp_done[b])                 # device input buffers of step i-2 are free
+            a, g = dev_in[b], dev_go[b]
+            for d_, h_ in zip(a, host_in):
+                d_.copy_(h_, non_blocking=True)
+            if g is not None:
+                g.copy_(host_go, non_blocking=True)
+            in_ready[b].record(s_in)
+        cur.wait_event(in_ready[b])
+        out = run_op(a, g)
+        comp_done[b].record(cur)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(comp_done[b])
+            s_out.wait_event(out_done[b])                  # host buffer of step i-2 has been written
+            host_outs[b].copy_(out, non_blocking=True)
+            out_done[b].record(s_out)
+        out.record_stream(s_out)
+        keep[b] = out
+
+    for i in range(min(args.warmup, 3)):
+        e2e_step(i)
     sync_all()
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
-    for _ in range(args.steps):
-        e2e_step()
+    s_in.wait_event(e_start)
+    s_out.wait_event(e_start)
+    for i in range(args.steps):
+        e2e_step(i)
+    cur.wait_stream(s_in)
+    cur.wait_stream(s_out)
     e_stop.record()
     sync_all()
     clocks = sampler.stop()
@@ -369,7 +404,9 @@ def run_ours(args):
                                       f"dp{world} (token shards, replicated experts, no collective)",
                        "l2": ("L2 flushed (256 MB write, then 256 MB read to drain the dirty lines) between steps; each step is a CUDA-graph replay of the op call timed by its own events" if decode
                               else f"expert weights ({weight_bytes / 1e9:.1f} GB) exceed the 126 MB L2; no flush")},
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "pipeline": ("host->device copy, op and device->host copy of consecutive steps overlap on three streams"
+                                 if pipelined else "one stream, copies and op in sequence")},
             "gpu_launches": args.steps * (2 if decode else 6 if w["mode"] == "fwd" else 14),
             "clocks": clocks,
             "achieved_tflops_whole_op": (6 if w["mode"] == "fwd" else 16) * S * H * H / (ms_step * 1e-3) / 1e12,
