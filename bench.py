@@ -51,6 +51,9 @@ WORKLOADS = {
     "gptoss120b_prefill_t16384": dict(T=16384, H=2880, E=128, K=4, mode="fwd", skew=True, ep=True),
     "gptoss20b_fwd_t8192_ep": dict(T=8192, H=2880, E=32, K=4, mode="fwd", ep=True),
     "gptoss20b_bwd_t8192_ep": dict(T=8192, H=2880, E=32, K=4, mode="bwd", ep=True),
+    # forward + backward through autograd: recomputing the forward (as the reference does) / keeping activations
+    "gptoss20b_train_t8192": dict(T=8192, H=2880, E=32, K=4, mode="train"),
+    "gptoss20b_train_saved_t8192": dict(T=8192, H=2880, E=32, K=4, mode="train", saved=True),
     "readme_fp32_t512": dict(T=512, H=2880, E=8, K=2, mode="fwd", fp32=True),
 }
 
@@ -119,7 +122,7 @@ def make_workload(name, weights_on=None):
     else:
         big = w["E"] * w["H"] * w["H"] * 3 > 2 ** 31          # 120B-shaped: draw the weights on the device
         inp = workloads.make_inputs(w["T"], w["H"], w["E"], w["K"], seed=42, dtype=dtype,
-                                    skew=w.get("skew", False), with_grad=(w["mode"] == "bwd"),
+                                    skew=w.get("skew", False), with_grad=(w["mode"] in ("bwd", "train")),
                                     weights_on=weights_on if big else None)
     return w, inp, dtype
 
@@ -139,9 +142,9 @@ def cpu_reference_time(w, inp, dtype, budget_s=20.0, threads=None):
     def run():
         t0 = time.perf_counter()
         with torch.no_grad():
-            if w["mode"] == "bwd":
+            if w["mode"] in ("bwd", "train"):
                 orc.experts_backward_oracle(inp["grad_out"], *args, cap, E, K, compute_dtype=dtype)
-            else:
+            if w["mode"] in ("fwd", "train"):
                 orc.experts_forward_oracle(*args, cap, E, K, compute_dtype=dtype)
         return time.perf_counter() - t0
 
@@ -166,9 +169,9 @@ def run_reference(args):
 
     def step():
         with torch.no_grad():
-            if w["mode"] == "bwd":
+            if w["mode"] in ("bwd", "train"):
                 orc.experts_backward_oracle(inp["grad_out"], *args_list, cap, w["E"], w["K"], compute_dtype=dtype)
-            else:
+            if w["mode"] in ("fwd", "train"):
                 orc.experts_forward_oracle(*args_list, cap, w["E"], w["K"], compute_dtype=dtype)
 
     steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
@@ -219,7 +222,10 @@ def run_ours(args):
     weight_bytes = float(sum(dev[i].numel() * dev[i].element_size() for i in (3, 4, 5, 6)))
     flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda") if decode else None
     flush_read = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda") if decode else None
-    grad_out = inp["grad_out"].cuda() if w["mode"] == "bwd" else None
+    grad_out = inp["grad_out"].cuda() if w["mode"] in ("bwd", "train") else None
+    if w["mode"] == "train":
+        for i in (0, 2, 3, 4, 5, 6):
+            dev[i].requires_grad_(True)
     L = _lib.lib()
     use_ep = bool(w.get("ep")) and world > 1
     if use_ep:
@@ -248,6 +254,12 @@ def run_ours(args):
             return ep.ep_experts(*dev, cap, E, K, stats=ep_stats)
         if w["mode"] == "bwd":
             return yamoe_b200.experts_backward(grad_out, *dev, cap, E, K)
+        if w["mode"] == "train":
+            for i in (0, 2, 3, 4, 5, 6):
+                dev[i].grad = None
+            out = yamoe_b200.experts_autograd(*dev, cap, E, K, True, save_activations=bool(w.get("saved")))
+            out.backward(grad_out)
+            return dev[0].grad
         return yamoe_b200.experts(*dev, cap, E, K)
 
     def sync_all():
@@ -314,7 +326,7 @@ def run_ours(args):
     # ---- end to end: host inputs in, host result out, every step -------------------------------
     host_in = [inp[k].pin_memory() for k in KEYS[:3]]
     host_out = torch.empty(T, H, dtype=dtype).pin_memory()
-    host_go = inp["grad_out"].pin_memory() if w["mode"] == "bwd" else None
+    host_go = inp["grad_out"].pin_memory() if w["mode"] in ("bwd", "train") else None
     h2d = sum(x.numel() * x.element_size() for x in host_in) + (host_go.numel() * host_go.element_size() if host_go is not None else 0)
     d2h = host_out.numel() * host_out.element_size()
 
@@ -334,6 +346,12 @@ def run_ours(args):
     dev_go = [torch.empty_like(host_go, device="cuda") if host_go is not None else None for _ in range(2)]
 
     def run_op(a, g):
+        if w["mode"] == "train":
+            x = a[0].detach().requires_grad_(True)
+            out = yamoe_b200.experts_autograd(x, a[1], a[2], *dev[3:], cap, E, K, False,
+                                              save_activations=bool(w.get("saved")))
+            out.backward(g)
+            return x.grad
         if w["mode"] == "bwd":
             outs = (ep.ep_experts_backward(g, *a, *dev[3:], cap, E, K) if use_ep
                     else yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K))
@@ -407,9 +425,9 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "pipeline": ("host->device copy, op and device->host copy of consecutive steps overlap on three streams"
                                  if pipelined else "one stream, copies and op in sequence")},
-            "gpu_launches": args.steps * (2 if decode else 6 if w["mode"] == "fwd" else 14),
+            "gpu_launches": args.steps * (2 if decode else {"fwd": 6, "bwd": 14, "train": 20}[w["mode"]]),
             "clocks": clocks,
-            "achieved_tflops_whole_op": (6 if w["mode"] == "fwd" else 16) * S * H * H / (ms_step * 1e-3) / 1e12,
+            "achieved_tflops_whole_op": {"fwd": 6, "bwd": 16, "train": 22}[w["mode"]] * S * H * H / (ms_step * 1e-3) / 1e12,
         }
         if gemm_ms and decode:
             mean_ms = sum(gemm_ms) / len(gemm_ms)

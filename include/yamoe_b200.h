@@ -228,6 +228,31 @@ int yamoe_b200_ep_return(const void *y_rows, void *const *peer_back, int64_t max
 int yamoe_b200_router_topk(const void *router_logits, int64_t *router_indices, void *router_scores, int64_t T,
                            int E, int K, int dtype, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Training pair that keeps activations instead of recomputing them (the reference's autograd
+ * wrapper saves only the seven inputs and recomputes the whole forward in backward,
+ * torch-ext/yamoe/layers.py:38-46, csrc/experts_backward.cu:176-199).
+ *   yamoe_b200_experts_forward_saving   same result as yamoe_b200_experts_forward; `saved` (sized by
+ *       yamoe_b200_backward_workspace_bytes, 256-byte aligned) receives the routing tables, the
+ *       gathered rows, the biased pre-activations and the weighted activations
+ *   yamoe_b200_experts_backward_saved   same gradients as yamoe_b200_experts_backward, reading them
+ *       from `saved` instead of running routing, gather and the gate_up GEMM again.  `saved` must
+ *       be untouched since the matching forward call with the same T, H, E, K, capacity and dtype;
+ *       it is also the scratch of this call and is consumed by it.
+ * ------------------------------------------------------------------------------------------- */
+int yamoe_b200_experts_forward_saving(const void *hidden_states, const int64_t *router_indices,
+                                      const void *routing_weights, int routing_cols, const void *gate_up_proj,
+                                      const void *gate_up_proj_bias, const void *down_proj,
+                                      const void *down_proj_bias, void *out, int64_t T, int H, int E, int K,
+                                      int64_t expert_capacity, int dtype, void *saved, size_t saved_bytes,
+                                      void *stream);
+int yamoe_b200_experts_backward_saved(const void *grad_out, int grad_out_per_slot, const void *routing_weights,
+                                      int routing_cols, const void *gate_up_proj, const void *down_proj,
+                                      const void *down_proj_bias, void *d_hidden, void *d_routing,
+                                      void *d_gate_up_proj, void *d_gate_up_proj_bias, void *d_down_proj,
+                                      void *d_down_proj_bias, int64_t T, int H, int E, int K, int64_t expert_capacity,
+                                      int dtype, void *saved, size_t saved_bytes, void *stream);
+
 /* Device status word of the last forward/backward call that used `workspace`: 0 when every
  * bounded device-side wait completed, otherwise a code naming the wait that gave up.  Reads
  * 4 bytes from the device with cudaMemcpyAsync on `stream` and synchronises that stream. */

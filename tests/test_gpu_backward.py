@@ -77,3 +77,26 @@ def test_autograd_function_end_to_end():
     orc.check_close(out.detach().cpu(), g["out_train"], RTOL_F32, "forward")
     for i, key in zip((0, 2, 3, 4, 5, 6), GRADS):
         orc.check_close(inp[i].grad.cpu(), g[key], RTOL_F32, key)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_saved_activation_pair_matches_recompute(dtype):
+    """forward_saving + backward_saved give the output and gradients of experts + experts_backward."""
+    import yamoe_b200
+    T, H, E, K = 700, 256, 8, 2
+    inp = orc.make_inputs(T, H, E, K, seed=21, weight_std=0.1, bias_std=0.2, dtype=dtype, with_grad=True)
+    keys = ["hidden_states", "router_indices", "routing_weights", "gate_up_proj", "gate_up_proj_bias",
+            "down_proj", "down_proj_bias"]
+    for cap in (T, 120):
+        dev = [inp[k].cuda() for k in keys]
+        for i in (0, 2, 3, 4, 5, 6):
+            dev[i].requires_grad_(True)
+        out = yamoe_b200.experts_autograd(*dev, cap, E, K, True, save_activations=True)
+        (out.float() * inp["grad_out"].cuda().float()).sum().backward()
+        ref_out = orc.experts_forward_oracle(*[inp[k] for k in keys], cap, E, K)
+        ref_g = orc.experts_backward_oracle(inp["grad_out"], *[inp[k] for k in keys], cap, E, K)
+        tol = RTOL_F32 if dtype == torch.float32 else RTOL_BF16
+        orc.check_close(out.detach().float().cpu(), ref_out, tol, f"saved-mode forward (capacity {cap})")
+        for i, r, name in zip((0, 2, 3, 4, 5, 6), ref_g, GRADS):
+            orc.check_close(dev[i].grad.float().cpu(), r, tol, f"saved-mode {name} (capacity {cap})",
+                            rel_l2=None if dtype == torch.float32 else 2e-2)

@@ -48,6 +48,10 @@ SIGNATURES = {
     "yamoe_b200_ep_local_forward": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "yamoe_b200_ep_return": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "yamoe_b200_router_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "yamoe_b200_experts_forward_saving": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 5 +
+                                          [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_experts_backward_saved": (c_int, [c_void_p, c_int, c_void_p, c_int] + [c_void_p] * 9 +
+                                          [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_device_status": (c_int, [c_void_p, c_void_p, ctypes.POINTER(ctypes.c_int32)]),
 }
 

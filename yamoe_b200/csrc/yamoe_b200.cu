@@ -235,12 +235,56 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
+// Forward pass that leaves what the backward pass needs in a workspace with the BACKWARD layout:
+// routing tables, xs, pre (biased pre-activations) and actw (weight * activation).  The
+// activation itself and the weighted output rows only live until the call returns; they borrow
+// the regions the backward pass later uses for gpre and gys.
+template <typename T>
+static int forward_train_impl(const void* hidden, const int64_t* ridx, const void* rw, int rcols, const void* wgu,
+                              const void* bgu, const void* wd, const void* bd, void* out, int64_t Tn, int H, int E,
+                              int K, int64_t cap, int dtype, void* ws, cudaStream_t st) {
+  Plan p = plan_backward(ws, Tn, H, E, K, dtype);
+  if (Tn == 0) return YAMOE_OK;
+  int rc = prepare_routing(p, st);
+  if (rc) return rc;
+  rc = launch_route<T>(ridx, reinterpret_cast<const T*>(rw), rcols, Tn, E, K, cap, p.rt, st);
+  if (rc) return rc;
+  const unsigned row_blocks = (unsigned)ceil_div(p.max_rows, kRowWarps);
+  gather_rows_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const T*>(hidden),
+                                                              reinterpret_cast<T*>(p.xs), p.rt.row_token,
+                                                              p.rt.header, H);
+  T* act = reinterpret_cast<T*>(p.gpre);
+  T* yrows = reinterpret_cast<T*>(p.gys);
+  EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), act, reinterpret_cast<T*>(p.actw), reinterpret_cast<T*>(p.pre),
+                p.rt.row_token, p.rt.row_weight, H};
+  EpiWeightedRows<T> wrows{reinterpret_cast<const T*>(bd), yrows, p.rt.row_token, p.rt.row_weight, H};
+  GemmArgs g1{p.xs, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, E,
+              p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  g1.pair_expert = p.rt.pair_expert; g1.pair_off = p.rt.pair_off;
+  GemmArgs g2{act, H, wd, H, (int64_t)H * H, 0, H, H, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
+  g2.pair_expert = p.rt.pair_expert; g2.pair_off = p.rt.pair_off;
+  if (use_tcgen05(current_path(), dtype, H)) {
+    if constexpr (sizeof(T) == 2) {
+      if ((rc = launch_umma<kFwd>(g1, glu, p.max_rows, p.max_tiles, st))) return rc;
+      if ((rc = launch_umma<kFwd>(g2, wrows, p.max_rows, p.max_tiles, st))) return rc;
+    }
+  } else {
+    launch_simt_gemm<T, kFwd>(g1, glu, p.max_rows, st);
+    launch_simt_gemm<T, kFwd>(g2, wrows, p.max_rows, st);
+  }
+  combine_padded_kernel<T><<<(unsigned)ceil_div(Tn, kRowWarps), kRowWarps * 32, 0, st>>>(
+      yrows, p.rt.flat_row, reinterpret_cast<T*>(out), Tn, H, K);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
 template <typename T>
 static int backward_impl(const void* grad_out, int per_slot, const void* hidden, const int64_t* ridx,
                          const void* rw, int rcols, const void* wgu, const void* bgu, const void* wd,
                          const void* bd, void* d_hidden, void* d_routing, void* d_wgu, void* d_bgu, void* d_wd,
                          void* d_bd, int64_t Tn, int H, int E, int K, int64_t cap, int dtype, void* ws,
-                         cudaStream_t st) {
+                         cudaStream_t st, bool saved = false) {
+  // saved: the workspace already holds the routing tables, xs, pre and actw of the forward pass
+  // (forward_train_impl); routing, the token gather and the gate_up recompute are skipped.
   Plan p = plan_backward(ws, Tn, H, E, K, dtype);
   const int path = current_path();
   const size_t es = sizeof(T);
@@ -254,14 +298,17 @@ static int backward_impl(const void* grad_out, int per_slot, const void* hidden,
     YB_CUDA_OK(cudaMemsetAsync(d_bd, 0, (size_t)E * H * es, st));
     return YAMOE_OK;
   }
-  int rc = prepare_routing(p, st);
-  if (rc) return rc;
-  rc = launch_route<T>(ridx, reinterpret_cast<const T*>(rw), rcols, Tn, E, K, cap, p.rt, st);
-  if (rc) return rc;
+  int rc = YAMOE_OK;
   const unsigned row_blocks = (unsigned)ceil_div(p.max_rows, kRowWarps);
-  gather_rows_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const T*>(hidden),
-                                                              reinterpret_cast<T*>(p.xs), p.rt.row_token,
-                                                              p.rt.header, H);
+  if (!saved) {
+    rc = prepare_routing(p, st);
+    if (rc) return rc;
+    rc = launch_route<T>(ridx, reinterpret_cast<const T*>(rw), rcols, Tn, E, K, cap, p.rt, st);
+    if (rc) return rc;
+    gather_rows_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const T*>(hidden),
+                                                                reinterpret_cast<T*>(p.xs), p.rt.row_token,
+                                                                p.rt.header, H);
+  }
   gather_grad_kernel<T><<<row_blocks, kRowWarps * 32, 0, st>>>(
       reinterpret_cast<const T*>(grad_out), per_slot ? K : 1, reinterpret_cast<const T*>(bd),
       reinterpret_cast<T*>(p.gys), p.gw_row, p.rt.row_token, p.rt.tile_expert, p.rt.header, H);
@@ -293,14 +340,14 @@ static int backward_impl(const void* grad_out, int per_slot, const void* hidden,
 
   if (use_tcgen05(path, dtype, H)) {
     if constexpr (sizeof(T) == 2) {
-      if ((rc = launch_umma<kFwd>(g1, glu, p.max_rows, p.max_tiles, st))) return rc;
+      if (!saved && (rc = launch_umma<kFwd>(g1, glu, p.max_rows, p.max_tiles, st))) return rc;
       if ((rc = launch_umma<kDgrad>(g2, glub, p.max_rows, p.max_tiles, st))) return rc;
       if ((rc = launch_umma<kWgrad>(g3, st_wd, p.max_rows, p.max_tiles, st))) return rc;
       if ((rc = launch_umma<kDgrad>(g4, sc_dh, p.max_rows, p.max_tiles, st))) return rc;
       if ((rc = launch_umma<kWgrad>(g5, st_wgu, p.max_rows, p.max_tiles, st))) return rc;
     }
   } else {
-    launch_simt_gemm<T, kFwd>(g1, glu, p.max_rows, st);
+    if (!saved) launch_simt_gemm<T, kFwd>(g1, glu, p.max_rows, st);
     launch_simt_gemm<T, kDgrad>(g2, glub, p.max_rows, st);
     launch_simt_gemm<T, kWgrad>(g3, st_wd, p.max_rows, st);
     launch_simt_gemm<T, kDgrad>(g4, sc_dh, p.max_rows, st);
@@ -819,6 +866,59 @@ int yamoe_b200_router_topk(const void* router_logits, int64_t* router_indices, v
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == YAMOE_BF16) return launch_router_topk<__nv_bfloat16>(router_logits, router_indices, router_scores, T, E, K, st);
   return launch_router_topk<float>(router_logits, router_indices, router_scores, T, E, K, st);
+}
+
+int yamoe_b200_experts_forward_saving(const void* hidden_states, const int64_t* router_indices,
+                                      const void* routing_weights, int routing_cols, const void* gate_up_proj,
+                                      const void* gate_up_proj_bias, const void* down_proj,
+                                      const void* down_proj_bias, void* out, int64_t T, int H, int E, int K,
+                                      int64_t expert_capacity, int dtype, void* saved, size_t saved_bytes,
+                                      void* stream) {
+  int rc = check_common(T, H, E, K, dtype);
+  if (rc) return rc;
+  if (routing_cols != E && routing_cols != K) return YAMOE_ERR_BAD_ARG;
+  if (expert_capacity < 0) return YAMOE_ERR_BAD_ARG;
+  if (T > 0 && (!hidden_states || !router_indices || !routing_weights || !out)) return YAMOE_ERR_BAD_ARG;
+  if (!gate_up_proj || !gate_up_proj_bias || !down_proj || !down_proj_bias) return YAMOE_ERR_BAD_ARG;
+  if (!saved || (reinterpret_cast<uintptr_t>(saved) & 255) ||
+      saved_bytes < yamoe_b200_backward_workspace_bytes(T, H, E, K, dtype))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == YAMOE_BF16)
+    return forward_train_impl<__nv_bfloat16>(hidden_states, router_indices, routing_weights, routing_cols,
+                                             gate_up_proj, gate_up_proj_bias, down_proj, down_proj_bias, out, T, H, E,
+                                             K, expert_capacity, dtype, saved, st);
+  return forward_train_impl<float>(hidden_states, router_indices, routing_weights, routing_cols, gate_up_proj,
+                                   gate_up_proj_bias, down_proj, down_proj_bias, out, T, H, E, K, expert_capacity,
+                                   dtype, saved, st);
+}
+
+int yamoe_b200_experts_backward_saved(const void* grad_out, int grad_out_per_slot, const void* routing_weights,
+                                      int routing_cols, const void* gate_up_proj, const void* down_proj,
+                                      const void* down_proj_bias, void* d_hidden, void* d_routing,
+                                      void* d_gate_up_proj, void* d_gate_up_proj_bias, void* d_down_proj,
+                                      void* d_down_proj_bias, int64_t T, int H, int E, int K, int64_t expert_capacity,
+                                      int dtype, void* saved, size_t saved_bytes, void* stream) {
+  int rc = check_common(T, H, E, K, dtype);
+  if (rc) return rc;
+  if (routing_cols != E && routing_cols != K) return YAMOE_ERR_BAD_ARG;
+  if (T > 0 && (!grad_out || !routing_weights || !d_hidden || !d_routing)) return YAMOE_ERR_BAD_ARG;
+  if (!gate_up_proj || !down_proj || !down_proj_bias || !d_gate_up_proj || !d_gate_up_proj_bias || !d_down_proj ||
+      !d_down_proj_bias)
+    return YAMOE_ERR_BAD_ARG;
+  if (!saved || (reinterpret_cast<uintptr_t>(saved) & 255) ||
+      saved_bytes < yamoe_b200_backward_workspace_bytes(T, H, E, K, dtype))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == YAMOE_BF16)
+    return backward_impl<__nv_bfloat16>(grad_out, grad_out_per_slot, nullptr, nullptr, routing_weights, routing_cols,
+                                        gate_up_proj, nullptr, down_proj, down_proj_bias, d_hidden, d_routing,
+                                        d_gate_up_proj, d_gate_up_proj_bias, d_down_proj, d_down_proj_bias, T, H, E, K,
+                                        expert_capacity, dtype, saved, st, true);
+  return backward_impl<float>(grad_out, grad_out_per_slot, nullptr, nullptr, routing_weights, routing_cols,
+                              gate_up_proj, nullptr, down_proj, down_proj_bias, d_hidden, d_routing, d_gate_up_proj,
+                              d_gate_up_proj_bias, d_down_proj, d_down_proj_bias, T, H, E, K, expert_capacity, dtype,
+                              saved, st, true);
 }
 
 int yamoe_b200_device_status(const void* workspace, void* stream, int32_t* status_out) {

@@ -29,11 +29,41 @@ class _ExpertsFn(torch.autograd.Function):
                 None, None, None, None)
 
 
+class _ExpertsSavedFn(torch.autograd.Function):
+    """Like `_ExpertsFn`, but the forward keeps the routing tables, gathered rows, pre-activations
+    and weighted activations (about 12*S*H bytes in bf16), and the backward skips routing, the
+    gather and the gate_up recompute: 12 instead of 16 S*H^2 of GEMM work."""
+
+    @staticmethod
+    def forward(ctx, hidden_flat, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias,
+                down_proj, down_proj_bias, expert_capacity, num_experts, top_k, enable_router_grads):
+        out, saved = ops.experts_forward_saving(hidden_flat, router_indices, routing_weights, gate_up_proj,
+                                                gate_up_proj_bias, down_proj, down_proj_bias, expert_capacity,
+                                                num_experts, top_k)
+        ctx.expert_capacity, ctx.num_experts, ctx.top_k = expert_capacity, num_experts, top_k
+        ctx.enable_router_grads = bool(enable_router_grads)
+        ctx.save_for_backward(saved, routing_weights, gate_up_proj, down_proj, down_proj_bias)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        saved, routing_weights, gate_up_proj, down_proj, down_proj_bias = ctx.saved_tensors
+        d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd = ops.experts_backward_saved(
+            grad_output, saved, routing_weights, gate_up_proj, down_proj, down_proj_bias, ctx.expert_capacity,
+            ctx.num_experts, ctx.top_k)
+        return (d_hidden, None, d_routing if ctx.enable_router_grads else None, d_wgu, d_bgu, d_wd, d_bd,
+                None, None, None, None)
+
+
 def experts_autograd(hidden_flat, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias, down_proj,
-                     down_proj_bias, expert_capacity, num_experts, top_k, enable_router_grads=True):
-    """Differentiable `experts`: forward through the CUDA op, backward through `experts_backward`."""
-    return _ExpertsFn.apply(hidden_flat, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias,
-                            down_proj, down_proj_bias, expert_capacity, num_experts, top_k, enable_router_grads)
+                     down_proj_bias, expert_capacity, num_experts, top_k, enable_router_grads=True,
+                     save_activations=False):
+    """Differentiable `experts`: forward through the CUDA op, backward through `experts_backward`
+    (recomputing the forward, like the reference) or, with `save_activations`, through the pair
+    that keeps the forward's intermediates.  A backward pass can run once per forward."""
+    fn = _ExpertsSavedFn if save_activations else _ExpertsFn
+    return fn.apply(hidden_flat, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias,
+                    down_proj, down_proj_bias, expert_capacity, num_experts, top_k, enable_router_grads)
 
 
 def ceil_div(a, b):

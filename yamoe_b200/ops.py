@@ -130,6 +130,62 @@ def _experts_backward_cuda(grad_out, hidden_states, router_indices, routing_weig
     return [d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd]
 
 
+def experts_forward_saving(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias,
+                           down_proj, down_proj_bias, expert_capacity, num_experts, top_k):
+    """`experts` that also returns the buffer `experts_backward_saved` needs (routing tables,
+    gathered rows, pre-activations, weighted activations), so that the backward pass does not
+    recompute the gate_up GEMM.  Returns (out, saved)."""
+    T, H, E, K = _validate(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias,
+                           down_proj, down_proj_bias, num_experts, top_k)
+    L = _lib.lib()
+    with torch.cuda.device(hidden_states.device):
+        hs = hidden_states.contiguous()
+        ri = router_indices.to(torch.int64).contiguous()
+        rw = routing_weights.contiguous()
+        wgu, bgu = gate_up_proj.contiguous(), gate_up_proj_bias.contiguous()
+        wd, bd = down_proj.contiguous(), down_proj_bias.contiguous()
+        out = torch.empty_like(hs)
+        dt = _DT[hs.dtype]
+        nbytes = L.yamoe_b200_backward_workspace_bytes(T, H, E, K, dt)
+        _require(nbytes > 0, "yamoe_b200: unsupported shape (H must be a positive multiple of 8, E <= 1024)")
+        saved = _workspace(nbytes, hs.device)
+        st = L.yamoe_b200_experts_forward_saving(hs.data_ptr(), ri.data_ptr(), rw.data_ptr(), rw.shape[1],
+                                                 wgu.data_ptr(), bgu.data_ptr(), wd.data_ptr(), bd.data_ptr(),
+                                                 out.data_ptr(), T, H, E, K, int(expert_capacity), dt,
+                                                 saved.data_ptr(), saved.numel(), _stream())
+        _lib.check(st, "experts_forward_saving")
+    return out, saved
+
+
+def experts_backward_saved(grad_out, saved, routing_weights, gate_up_proj, down_proj, down_proj_bias,
+                           expert_capacity, num_experts, top_k):
+    """Gradients (same six tensors as `experts_backward`) from the buffer left by
+    `experts_forward_saving`; the buffer is consumed."""
+    T, H = grad_out.numel() // gate_up_proj.shape[1], gate_up_proj.shape[1]
+    E, K = int(num_experts), int(top_k)
+    per_slot = 0
+    if grad_out.numel() == routing_weights.shape[0] * K * H and K != 1:
+        per_slot, T = 1, routing_weights.shape[0]
+    _require(grad_out.is_cuda and grad_out.dtype in _DT, "grad_out must be a CUDA float32/bfloat16 tensor")
+    L = _lib.lib()
+    with torch.cuda.device(grad_out.device):
+        go = grad_out.contiguous()
+        rw = routing_weights.contiguous()
+        wgu, wd, bd = gate_up_proj.contiguous(), down_proj.contiguous(), down_proj_bias.contiguous()
+        d_hidden = torch.empty(T, H, dtype=go.dtype, device=go.device)
+        d_routing = torch.empty_like(rw)
+        d_wgu = torch.empty_like(wgu)
+        d_bgu = torch.empty(E, 2 * H, dtype=go.dtype, device=go.device)
+        d_wd, d_bd = torch.empty_like(wd), torch.empty_like(bd)
+        st = L.yamoe_b200_experts_backward_saved(go.data_ptr(), per_slot, rw.data_ptr(), rw.shape[1], wgu.data_ptr(),
+                                                 wd.data_ptr(), bd.data_ptr(), d_hidden.data_ptr(), d_routing.data_ptr(),
+                                                 d_wgu.data_ptr(), d_bgu.data_ptr(), d_wd.data_ptr(), d_bd.data_ptr(),
+                                                 T, H, E, K, int(expert_capacity), _DT[go.dtype], saved.data_ptr(),
+                                                 saved.numel(), _stream())
+        _lib.check(st, "experts_backward_saved")
+    return [d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd]
+
+
 def route(router_indices: torch.Tensor, num_experts: int):
     """Stable sort of the flattened assignments by expert id plus histogram and inclusive
     prefix sums: (sorted_values, sorted_indices, bins[E+1], counts[E]), all int32."""
