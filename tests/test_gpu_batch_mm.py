@@ -55,8 +55,10 @@ def test_batch_mm_fp32():
     orc.check_close(out.cpu(), torch.bmm(x, w), 1e-5, "batch_mm fp32")
 
 
-def test_two_cta_kernel_in_subprocess():
-    """The cta_group::2 variant is selected by an environment variable read once per process."""
+@pytest.mark.parametrize("switch", ["YAMOE_B200_2CTA", "YAMOE_B200_FUSED_GATHER"])
+def test_opt_in_kernel_variants_in_subprocess(switch):
+    """The cta_group::2 GEMM and the TMA-gather-fused gate_up GEMM are selected by environment
+    variables read once per process."""
     import os
     import subprocess
     import sys
@@ -79,6 +81,7 @@ def test_two_cta_kernel_in_subprocess():
         "orc.check_close(o.float().cpu(), ref, 2e-2, 'two-CTA forward', rel_l2=1e-2)\n"
         "print('ok')\n")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, YAMOE_B200_2CTA="1", PYTHONPATH=root)
+    env = dict(os.environ, PYTHONPATH=root)
+    env[switch] = "1"
     res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0 and "ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

@@ -87,6 +87,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+// Four rows of a 2D tensor, picked by index, into four consecutive 128-byte shared-memory rows
+// (tensor map box {64, 1}; same swizzled layout as a tiled load of four adjacent rows).
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int c0, int r0, int r1, int r2,
+                                            int r3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -142,6 +150,7 @@ struct UmmaParams {
   const int32_t* tile_expert;
   const int32_t* pad_off;
   int32_t* header;
+  const int32_t* gather_rows;   // kFwd: source row of every padded row (TMA gather of A), or null
 };
 
 template <int BN>
@@ -231,7 +240,44 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // =========================== TMA producer ================================================
-    if (lane == 0) {
+    if (MODE == kFwd && p.gather_rows != nullptr) {
+      // Gather-fused A operand: the whole warp works.  Lane j fetches rows 4j..4j+3 of the tile
+      // straight from the un-permuted source with one TMA gather per k-block; lane 0 also arms the
+      // barrier and loads B.  The permuted activations never exist in global memory.
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
+        int e, row0, n0, krow, kblocks;
+        decode(id, e, row0, n0, krow, kblocks);
+        int4 r = *reinterpret_cast<const int4*>(p.gather_rows + row0 + 4 * lane);
+        r.x = max(r.x, 0); r.y = max(r.y, 0); r.z = max(r.z, 0); r.w = max(r.w, 0);   // padding rows: any valid row
+        for (int kb = 0; kb < kblocks; ++kb) {
+          int good = 1;
+          if (lane == 0) good = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag) ? 1 : 0;
+          good = __shfl_sync(0xffffffffu, good, 0);
+          if (!good) {
+            if (lane == 0) {
+              abort_flag = 1;
+              atomicMax(p.header + kHdrStatus, (int)kStatusProducerTimeout);
+            }
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          const uint32_t sa = smem_base + stage * SM::kStageBytes;
+          const uint32_t sb = sa + SM::kABytes;
+          if (lane == 0) {
+            mbar_expect_tx(full, SM::kStageBytes);
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_3d(sb + i * 8192, &tmB, n0 + i * 64, kb * kUmmaBK, e, full);
+          }
+          __syncwarp();
+          tma_gather4(sa + lane * 512, &tmA, kb * kUmmaBK, r.x, r.y, r.z, r.w, full);
+          if (++stage == kUmmaStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    } else if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -457,8 +503,10 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
     const uint64_t db[2] = {(uint64_t)g.N, (uint64_t)max_rows}, sb[1] = {(uint64_t)g.ldb * 2};
     ok = ok && make_map(&tmB, g.B, 2, db, sb, ba);
   } else {
-    const uint64_t da[2] = {(uint64_t)g.K, (uint64_t)max_rows}, sa[1] = {(uint64_t)g.lda * 2};
-    const uint32_t ba[2] = {64, 128};
+    const bool gather = MODE == kFwd && g.gather_rows != nullptr;
+    const uint64_t da[2] = {(uint64_t)g.K, (uint64_t)(gather ? g.gather_src_rows : max_rows)};
+    const uint64_t sa[1] = {(uint64_t)g.lda * 2};
+    const uint32_t ba[2] = {64, gather ? 1u : 128u};      // gather: one row per index, four indices per copy
     ok = ok && make_map(&tmA, g.A, 2, da, sa, ba);
     if (MODE == kFwd) {
       const uint64_t db[3] = {(uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.E};
@@ -480,7 +528,8 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
       return YAMOE_ERR_CUDA;
     attr_done = true;
   }
-  UmmaParams p{g.M, g.N, g.K, g.E, g.tile_expert, g.pad_off, const_cast<int32_t*>(g.header)};
+  UmmaParams p{g.M, g.N, g.K, g.E, g.tile_expert, g.pad_off, const_cast<int32_t*>(g.header),
+               MODE == kFwd ? g.gather_rows : nullptr};
   const int NT = (int)ceil_div(g.N, BN);
   int64_t total_max = MODE == kWgrad ? (int64_t)g.E * ceil_div(g.M, kUmmaBM) * NT : max_tiles * NT;
   int grid = (int)std::min<int64_t>(total_max, umma_sm_count());

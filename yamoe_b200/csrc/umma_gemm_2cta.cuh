@@ -324,7 +324,7 @@ inline int launch_umma_gemm_2cta(const GemmArgs& g, const Epi& epi, int64_t max_
 template <int MODE, class Epi>
 inline int launch_umma(const GemmArgs& g, const Epi& epi, int64_t max_rows, int64_t max_tiles, cudaStream_t stream) {
   if constexpr (MODE != kWgrad) {
-    if (umma_2cta_enabled() && g.pair_expert != nullptr && g.pair_off != nullptr)
+    if (umma_2cta_enabled() && g.pair_expert != nullptr && g.pair_off != nullptr && g.gather_rows == nullptr)
       return launch_umma_gemm_2cta<MODE>(g, epi, max_rows, max_tiles, stream);
   }
   return launch_umma_gemm<MODE>(g, epi, max_rows, max_tiles, stream);
