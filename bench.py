@@ -127,7 +127,7 @@ def make_workload(name, weights_on=None):
     return w, inp, dtype
 
 
-def cpu_reference_time(w, inp, dtype, budget_s=20.0, threads=None):
+def cpu_reference_time(w, inp, dtype, limit_s=20.0, threads=None):
     """Times the CPU port of the reference forward (sparse per-expert loop) in the workload's
     dtype.  Returns (tokens_per_s, cores, sample description)."""
     import torch
@@ -149,8 +149,8 @@ def cpu_reference_time(w, inp, dtype, budget_s=20.0, threads=None):
         return time.perf_counter() - t0
 
     first = run()                               # warm-up, also sizes the sample
-    reps = max(1, min(3, int(budget_s / max(first, 1e-3)) - 1))
-    best = min([run() for _ in range(reps)] + ([first] if reps == 1 and first > budget_s / 2 else []))
+    reps = max(1, min(3, int(limit_s / max(first, 1e-3)) - 1))
+    best = min([run() for _ in range(reps)] + ([first] if reps == 1 and first > limit_s / 2 else []))
     return T / best, cores, f"full workload ({T} tokens), best of {reps} after 1 warm-up, {dtype}, {cores} threads"
 
 

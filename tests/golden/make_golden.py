@@ -60,7 +60,9 @@ def small_inputs(T, H, E, K, seed, with_grad=True):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     reference = load(os.path.join(ref_root, "build/torch28-cxx11-cu129-x86_64-linux/yamoe/reference.py"), "ref_reference")
     twin = load(os.path.join(ref_root, "torch-ext/yamoe/vendored/gpt_oss_mlp.py"), "ref_gpt_oss_mlp")
     yref = load(os.path.join(ref_root, "torch-ext/yamoe/vendored/yamoe_ref.py"), "ref_yamoe_ref")
