@@ -241,12 +241,15 @@ def run_ours(args):
         T = hi - lo
         ep_stats = {}
         peer_ctx = None
-        if args.ep_mode in ("peer", "peer-fused") and w["mode"] == "fwd":
+        if args.ep_mode in ("peer", "peer-fused") and w["mode"] in ("fwd", "bwd"):
             peer_ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=T_total, max_tokens_local=T, dtype=dtype,
-                                             fused_return=(args.ep_mode == "peer-fused"))
+                                             fused_return=(args.ep_mode == "peer-fused"),
+                                             backward=(w["mode"] == "bwd"))
 
     def step():
         if use_ep and w["mode"] == "bwd":
+            if peer_ctx is not None:
+                return peer_ctx.backward(grad_out, *dev, cap)
             return ep.ep_experts_backward(grad_out, *dev, cap, E, K)
         if use_ep and peer_ctx is not None:
             return peer_ctx.forward(*dev, cap)
@@ -353,8 +356,11 @@ def run_ours(args):
             out.backward(g)
             return x.grad
         if w["mode"] == "bwd":
-            outs = (ep.ep_experts_backward(g, *a, *dev[3:], cap, E, K) if use_ep
-                    else yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K))
+            if use_ep:
+                outs = (peer_ctx.backward(g, *a, *dev[3:], cap) if peer_ctx is not None
+                        else ep.ep_experts_backward(g, *a, *dev[3:], cap, E, K))
+            else:
+                outs = yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K)
             return outs[0]
         if use_ep:
             return peer_ctx.forward(*a, *dev[3:], cap) if peer_ctx is not None else ep.ep_experts(*a, *dev[3:], cap, E, K)

@@ -218,6 +218,34 @@ int yamoe_b200_ep_local_forward(const void *recv_x, const void *gate_up_proj, co
 int yamoe_b200_ep_return(const void *y_rows, void *const *peer_back, int64_t max_rows, int H, int E, int G,
                          int dtype, const void *workspace, void *stream);
 
+/* Backward over the same peer buffers.  Three more symmetric buffers per rank: recv_g
+ * [max_rows, H] (upstream-gradient rows), recv_w [max_rows] fp32 (routing weight of every row)
+ * and back_w [S_local] fp32 (routing-weight gradients on their way home).  The workspace is the
+ * forward one with more behind it (yamoe_b200_ep_backward_workspace_bytes), so plan and dispatch
+ * take it unchanged.  One call is:
+ *   route, all-gather of counts, yamoe_b200_ep_plan (peer_back = the d_hidden row buffers)
+ *   yamoe_b200_ep_dispatch(hidden -> recv_x), yamoe_b200_ep_dispatch(grad_out -> recv_g),
+ *   yamoe_b200_ep_dispatch_weights(routing_weights [T, routing_cols] -> recv_w)
+ *   (barrier)
+ *   yamoe_b200_ep_local_backward   recompute, the four gradient GEMMs and both bias gradients for
+ *                                  the local experts; the input-gradient rows leave through the
+ *                                  last data-gradient GEMM's epilogue into peer_back, the
+ *                                  routing-weight gradients into peer_back_w
+ *   (barrier)                      then yamoe_b200_combine_rows with unit weights on `back`
+ *                                  (= d_hidden) and a scatter of back_w through sorted_indices.
+ * Weight and bias gradients stay with the expert's owner: experts are not replicated. */
+size_t yamoe_b200_ep_backward_workspace_bytes(int64_t max_rows, int H, int E, int G, int dtype);
+int yamoe_b200_ep_dispatch_weights(const void *routing_weights, int routing_cols, const int32_t *sorted_values,
+                                   const int32_t *sorted_indices, const int32_t *bins, int64_t S,
+                                   void *const *peer_recv_w, int64_t max_rows, int H, int E, int G, int K, int dtype,
+                                   const void *workspace, void *stream);
+int yamoe_b200_ep_local_backward(const void *recv_x, const void *recv_g, const float *recv_w,
+                                 const void *gate_up_proj, const void *gate_up_proj_bias, const void *down_proj,
+                                 const void *down_proj_bias, void *d_gate_up_proj, void *d_gate_up_proj_bias,
+                                 void *d_down_proj, void *d_down_proj_bias, void *const *peer_back_w,
+                                 int64_t expert_capacity, int64_t max_rows, int H, int E, int G, int dtype,
+                                 void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Router tail of the layer that calls the expert op.  Replaces the top-k / softmax / scatter
  * chain of Yamoe.forward (torch-ext/yamoe/layers.py:136-149):

@@ -158,3 +158,80 @@ def test_peer_store_ep_two_gpus(fused):
         ref = orc.experts_forward_oracle(*[inp[k] for k in KEYS], cap, E, K)
         got = torch.cat([r[1][i] for r in results])
         orc.check_close(got, ref, 2e-2, f"peer-store expert parallel, call {i}", rel_l2=1e-2)
+
+
+PEER_BWD_CASES = ((1024, 1024, False, 9, True), (1024, 100, True, 10, False), (512, 512, True, 11, True))
+
+
+def _peer_bwd_worker(rank, world, port, q):
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from yamoe_b200 import ep, workloads
+        H, E, K = 256, 16, 4
+        ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=1024, max_tokens_local=512, dtype=torch.bfloat16,
+                                    backward=True)
+        outs = []
+        # forward and backward alternate on the same buffers; dense and [T, K] routing weights
+        for T, cap, skew, seed, dense in PEER_BWD_CASES:
+            inp = workloads.make_inputs(T, H, E, K, seed=seed, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16,
+                                        skew=skew, with_grad=True)
+            lo, hi = rank * (T // world), (rank + 1) * (T // world)
+            local_w = ep.shard_expert_weights(*[inp[k].cuda() for k in KEYS[3:]], rank, world)
+            ri = inp["router_indices"][lo:hi].cuda()
+            rw = inp["routing_weights"][lo:hi].cuda()
+            if not dense:
+                rw = torch.gather(rw, 1, ri).contiguous()
+            out = ctx.forward(inp["hidden_states"][lo:hi].cuda(), ri, rw, *local_w, cap)
+            grads = ctx.backward(inp["grad_out"][lo:hi].cuda(), inp["hidden_states"][lo:hi].cuda(), ri, rw,
+                                 *local_w, cap)
+            torch.cuda.synchronize()
+            outs.append((out.float().cpu(), [g.float().cpu() for g in grads]))
+        q.put((rank, outs, True))
+        dist.barrier()
+    except Exception as exc:
+        q.put((rank, repr(exc), None))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_store_ep_backward_two_gpus():
+    """Backward over peer stores: token rows, gradient rows and routing weights go to the expert
+    owners, input-gradient rows return through the data-gradient GEMM's epilogue."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from oracle import experts_oracle as orc
+    from yamoe_b200 import workloads
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + os.getpid() % 1000
+    procs = [ctx.Process(target=_peer_bwd_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(2)]
+    bad = [r for r in results if r[2] is None]
+    if bad:
+        for p in procs:
+            p.terminate()
+        pytest.fail(f"rank {bad[0][0]}: {bad[0][1]}")
+    for p in procs:
+        p.join(timeout=60)
+    results.sort(key=lambda x: x[0])
+    H, E, K = 256, 16, 4
+    for i, (T, cap, skew, seed, dense) in enumerate(PEER_BWD_CASES):
+        inp = workloads.make_inputs(T, H, E, K, seed=seed, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16,
+                                    skew=skew, with_grad=True)
+        ref = orc.experts_forward_oracle(*[inp[k] for k in KEYS], cap, E, K)
+        got = torch.cat([r[1][i][0] for r in results])
+        orc.check_close(got, ref, 2e-2, f"peer-store forward, call {i}", rel_l2=1e-2)
+        ref_g = list(orc.experts_backward_oracle(inp["grad_out"], *[inp[k] for k in KEYS], cap, E, K))
+        if not dense:
+            ref_g[1] = torch.gather(ref_g[1], 1, inp["router_indices"])
+        for j, name in enumerate(["d_hidden", "d_routing", "d_wgu", "d_bgu", "d_wd", "d_bd"]):
+            got_g = torch.cat([r[1][i][1][j] for r in results])
+            orc.check_close(got_g, ref_g[j], 2e-2, f"peer-store backward {name}, call {i}", rel_l2=2e-2)

@@ -47,6 +47,11 @@ SIGNATURES = {
                                        c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "yamoe_b200_ep_local_forward": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "yamoe_b200_ep_return": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "yamoe_b200_ep_backward_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
+    "yamoe_b200_ep_dispatch_weights": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                               c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "yamoe_b200_ep_local_backward": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int, c_int,
+                                                               c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_router_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "yamoe_b200_experts_forward_saving": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 5 +
                                           [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),

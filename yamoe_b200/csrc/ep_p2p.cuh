@@ -17,6 +17,10 @@
 //   ep_rowtables_kernel   validity of every local row (padding and rows beyond the capacity)
 //   ep_dispatch_kernel    hidden[token] -> recv_x of the owner, one warp per row, 16-byte stores
 //   ep_return_kernel      y rows -> back_y of the source rank (zeros for dropped rows)
+// The backward pass travels the same way: token rows and upstream-gradient rows with the row
+// dispatch kernel, the routing weight of every assignment with ep_dispatch_weight_kernel; the
+// input-gradient rows return through the dgrad GEMM's epilogue (EpiPeerRows without a bias) and
+// the routing-weight gradients with ep_return_scalar_kernel.
 // Peer loads are never used and nothing here waits on another GPU: the phases are separated by
 // stream-ordered collectives issued by the host binding.
 #pragma once
@@ -141,7 +145,7 @@ __global__ void ep_rowtables_kernel(EpTables t, int64_t capacity, int64_t max_ro
 // rows dropped by the capacity send zeros, padding rows send nothing.
 template <typename T>
 struct EpiPeerRows {
-  const T* bias;             // [per, N]
+  const T* bias;             // [per, N], or nullptr
   const int64_t* row_dest;
   const int32_t* row_token;
   int N;
@@ -154,10 +158,13 @@ struct EpiPeerRows {
     if (row_token[row] < 0) {
 #pragma unroll
       for (int i = 0; i < NV; ++i) o[i] = 0.f;
-    } else {
+    } else if (bias != nullptr) {
       load_vec<T, NV>(bias + (size_t)e * N + n0, o);
 #pragma unroll
       for (int i = 0; i < NV; ++i) o[i] += v[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] = v[i];
     }
     store_vec<T, NV>(reinterpret_cast<T*>(dest) + n0, o);
   }
@@ -203,6 +210,44 @@ ep_return_kernel(const T* __restrict__ y, EpTables t, void* const* __restrict__ 
     const uint4* src = reinterpret_cast<const uint4*>(y + (size_t)r * H);
     for (int v = lane; v < nvec; v += 32) d[v] = src[v];
   }
+}
+
+// One thread per sorted assignment j: its routing weight (fp32) goes to the owner's recv_w at
+// the row its token row went to.  routing_cols == E: dense [T, E] weights, else [T, K].
+template <typename T>
+__global__ void ep_dispatch_weight_kernel(const T* __restrict__ routing_weights, int routing_cols,
+                                          const int32_t* __restrict__ sorted_values,
+                                          const int32_t* __restrict__ sorted_indices,
+                                          const int32_t* __restrict__ bins, const int32_t* __restrict__ dest_row,
+                                          void* const* __restrict__ peer_w, int64_t S, int E, int per, int K) {
+  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= S || j >= bins[E - 1]) return;
+  const int e = sorted_values[j];
+  const int i = (int)j - (e ? bins[e - 1] : 0);
+  const int flat = sorted_indices[j];
+  const size_t idx = routing_cols == E ? (size_t)(flat / K) * E + e : (size_t)flat;
+  reinterpret_cast<float*>(peer_w[e / per])[dest_row[e] + i] = DT<T>::ld(routing_weights + idx);
+}
+
+// row_weight[r] = received routing weight for kept rows, 0 for padding and dropped rows.
+__global__ void ep_load_weights_kernel(EpTables t, const float* __restrict__ recv_w, int64_t max_rows) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= max_rows) return;
+  t.rt.row_weight[r] = t.rt.row_token[r] >= 0 ? recv_w[r] : 0.f;
+}
+
+// One thread per local row: val[row] (fp32) goes back to the rank the row came from, at the
+// position of the assignment in that rank's sorted order.  Padding rows send nothing.
+__global__ void ep_return_scalar_kernel(const float* __restrict__ val, EpTables t,
+                                        void* const* __restrict__ peer_back_w, int G, int per) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= t.rt.header[kHdrRowsUsed]) return;
+  const int le = t.rt.tile_expert[r / kTileM];
+  if (r - t.rt.pad_off[le] >= t.rt.counts[le]) return;
+  int s = 0;
+  while (s + 1 < G && t.seg_row[(s + 1) * per + le] <= r) ++s;
+  const int64_t dst_row = (int64_t)t.src_start[s * per + le] + (r - t.seg_row[s * per + le]);
+  reinterpret_cast<float*>(peer_back_w[s])[dst_row] = t.rt.row_token[r] >= 0 ? val[r] : 0.f;
 }
 
 }  // namespace yb

@@ -448,10 +448,15 @@ static int batch_mm_impl(const void* x, const void* w, void* out, int E, int C, 
 struct EpPlan {
   EpTables t;
   void* act = nullptr;     // [max_rows, H]
+  // backward only (the tables and `act` above sit at the same offsets in both layouts)
+  void* gys = nullptr;     // [max_rows, H]   upstream-gradient rows, zero where not kept
+  void* pre = nullptr;     // [max_rows, 2H]
+  void* gpre = nullptr;    // [max_rows, 2H]
+  float* gw_row = nullptr; // [max_rows]
   size_t bytes = 0;
 };
 
-static EpPlan plan_ep(void* ws, int64_t max_rows, int H, int E, int G, int dtype) {
+static EpPlan plan_ep(void* ws, int64_t max_rows, int H, int E, int G, int dtype, bool backward = false) {
   EpPlan p;
   Bump b(ws);
   const int per = E / G;
@@ -471,7 +476,14 @@ static EpPlan plan_ep(void* ws, int64_t max_rows, int H, int E, int G, int dtype
   p.t.src_start = b.take<int32_t>((size_t)G * per);
   p.t.seg_row = b.take<int32_t>((size_t)G * per);
   p.t.row_dest = b.take<int64_t>(max_rows);
-  p.act = b.take<char>((size_t)max_rows * H * (dtype == YAMOE_BF16 ? 2 : 4));
+  const size_t es = dtype == YAMOE_BF16 ? 2 : 4;
+  p.act = b.take<char>((size_t)max_rows * H * es);
+  if (backward) {
+    p.gys = b.take<char>((size_t)max_rows * H * es);
+    p.pre = b.take<char>((size_t)max_rows * 2 * H * es);
+    p.gpre = b.take<char>((size_t)max_rows * 2 * H * es);
+    p.gw_row = b.take<float>(max_rows);
+  }
   p.bytes = b.off + 256;
   return p;
 }
@@ -518,6 +530,64 @@ static int ep_local_forward_impl(const void* recv_x, const void* wgu, const void
     if (fused) launch_simt_gemm<T, kFwd>(g2, prows, max_rows, st);
     else launch_simt_gemm<T, kFwd>(g2, wrows, max_rows, st);
   }
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+// Backward of the local problem on the rows peers stored here: recv_x (token rows), recv_g
+// (upstream-gradient rows) and recv_w (routing weights), all in the padded layout of the plan.
+// Input-gradient rows leave through the last dgrad GEMM's epilogue into the source ranks' buffers
+// (row_dest of the plan), routing-weight gradients through ep_return_scalar_kernel.
+template <typename T>
+static int ep_local_backward_impl(const void* recv_x, const void* recv_g, const float* recv_w, const void* wgu,
+                                  const void* bgu, const void* wd, const void* bd, void* d_wgu, void* d_bgu,
+                                  void* d_wd, void* d_bd, void* const* peer_back_w, int64_t cap, int64_t max_rows,
+                                  int H, int per, int G, int dtype, const EpPlan& p, cudaStream_t st) {
+  const RouteTables& rt = p.t.rt;
+  const int64_t max_tiles = max_rows / kTileM;
+  ep_load_weights_kernel<<<(unsigned)ceil_div(max_rows, 256), 256, 0, st>>>(p.t, recv_w, max_rows);
+  gather_grad_kernel<T><<<(unsigned)ceil_div(max_rows, kRowWarps), kRowWarps * 32, 0, st>>>(
+      reinterpret_cast<const T*>(recv_g), 1, reinterpret_cast<const T*>(bd), reinterpret_cast<T*>(p.gys), p.gw_row,
+      rt.row_token, rt.tile_expert, rt.header, H);
+  auto with_pairs = [&](GemmArgs g) { g.pair_expert = rt.pair_expert; g.pair_off = rt.pair_off; return g; };
+  EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), nullptr, reinterpret_cast<T*>(p.act), reinterpret_cast<T*>(p.pre),
+                rt.row_token, rt.row_weight, H};
+  const GemmArgs g1 = with_pairs(GemmArgs{recv_x, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, per,
+                                          rt.tile_expert, rt.pad_off, rt.header});
+  EpiGluBackward<T> glub{reinterpret_cast<const T*>(p.pre), reinterpret_cast<T*>(p.gpre), p.gw_row, rt.row_token,
+                         rt.row_weight, H};
+  const GemmArgs g2 = with_pairs(GemmArgs{p.gys, H, wd, H, (int64_t)H * H, 0, H, H, per, rt.tile_expert, rt.pad_off,
+                                          rt.header});
+  EpiStore<T> st_wd{reinterpret_cast<T*>(d_wd), H, H};
+  const GemmArgs g3 = with_pairs(GemmArgs{p.act, H, p.gys, H, 0, H, H, 0, per, rt.tile_expert, rt.pad_off,
+                                          rt.header});
+  EpiPeerRows<T> prows{nullptr, p.t.row_dest, rt.row_token, H};
+  const GemmArgs g4 = with_pairs(GemmArgs{p.gpre, 2 * (int64_t)H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, H,
+                                          2 * H, per, rt.tile_expert, rt.pad_off, rt.header});
+  EpiStore<T> st_wgu{reinterpret_cast<T*>(d_wgu), H, 2 * H};
+  const GemmArgs g5 = with_pairs(GemmArgs{recv_x, H, p.gpre, 2 * (int64_t)H, 0, H, 2 * H, 0, per, rt.tile_expert,
+                                          rt.pad_off, rt.header});
+  int rc = YAMOE_OK;
+  if (use_tcgen05(current_path(), dtype, H)) {
+    if constexpr (sizeof(T) == 2) {
+      if ((rc = launch_umma<kFwd>(g1, glu, max_rows, max_tiles, st))) return rc;
+      if ((rc = launch_umma<kDgrad>(g2, glub, max_rows, max_tiles, st))) return rc;
+      if ((rc = launch_umma<kWgrad>(g3, st_wd, max_rows, max_tiles, st))) return rc;
+      if ((rc = launch_umma<kDgrad>(g4, prows, max_rows, max_tiles, st))) return rc;
+      if ((rc = launch_umma<kWgrad>(g5, st_wgu, max_rows, max_tiles, st))) return rc;
+    }
+  } else {
+    launch_simt_gemm<T, kFwd>(g1, glu, max_rows, st);
+    launch_simt_gemm<T, kDgrad>(g2, glub, max_rows, st);
+    launch_simt_gemm<T, kWgrad>(g3, st_wd, max_rows, st);
+    launch_simt_gemm<T, kDgrad>(g4, prows, max_rows, st);
+    launch_simt_gemm<T, kWgrad>(g5, st_wgu, max_rows, st);
+  }
+  colsum_kernel<T, true><<<dim3((unsigned)ceil_div(H, 512 / (int)sizeof(T)), per), 256, 0, st>>>(
+      reinterpret_cast<const T*>(p.gys), rt.row_weight, rt.pad_off, rt.counts, cap, reinterpret_cast<T*>(d_bd), H);
+  colsum_kernel<T, false><<<dim3((unsigned)ceil_div(2 * H, 512 / (int)sizeof(T)), per), 256, 0, st>>>(
+      reinterpret_cast<const T*>(p.gpre), rt.row_weight, rt.pad_off, rt.counts, cap, reinterpret_cast<T*>(d_bgu),
+      2 * H);
+  ep_return_scalar_kernel<<<(unsigned)ceil_div(max_rows, 256), 256, 0, st>>>(p.gw_row, p.t, peer_back_w, G, per);
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
@@ -875,6 +945,63 @@ int yamoe_b200_ep_return(const void* y_rows, void* const* peer_back, int64_t max
     ep_return_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const float*>(y_rows), p.t,
                                                               peer_back, H, G, E / G);
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+size_t yamoe_b200_ep_backward_workspace_bytes(int64_t max_rows, int H, int E, int G, int dtype) {
+  if (check_ep(max_rows, H, E, G, 0, dtype)) return 0;
+  return plan_ep(nullptr, max_rows, H, E, G, dtype, true).bytes;
+}
+
+int yamoe_b200_ep_dispatch_weights(const void* routing_weights, int routing_cols, const int32_t* sorted_values,
+                                   const int32_t* sorted_indices, const int32_t* bins, int64_t S,
+                                   void* const* peer_recv_w, int64_t max_rows, int H, int E, int G, int K, int dtype,
+                                   const void* workspace, void* stream) {
+  int rc = check_ep(max_rows, H, E, G, 0, dtype);
+  if (rc) return rc;
+  if (S == 0) return YAMOE_OK;
+  if (!routing_weights || !sorted_values || !sorted_indices || !bins || !peer_recv_w || !workspace || K <= 0 ||
+      S < 0 || (routing_cols != E && routing_cols != K))
+    return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  EpPlan p = plan_ep(const_cast<void*>(workspace), max_rows, H, E, G, dtype);
+  const unsigned blocks = (unsigned)ceil_div(S, 256);
+  if (dtype == YAMOE_BF16)
+    ep_dispatch_weight_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(routing_weights), routing_cols, sorted_values, sorted_indices, bins,
+        p.t.dest_row, peer_recv_w, S, E, E / G, K);
+  else
+    ep_dispatch_weight_kernel<float><<<blocks, 256, 0, st>>>(
+        reinterpret_cast<const float*>(routing_weights), routing_cols, sorted_values, sorted_indices, bins,
+        p.t.dest_row, peer_recv_w, S, E, E / G, K);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+int yamoe_b200_ep_local_backward(const void* recv_x, const void* recv_g, const float* recv_w,
+                                 const void* gate_up_proj, const void* gate_up_proj_bias, const void* down_proj,
+                                 const void* down_proj_bias, void* d_gate_up_proj, void* d_gate_up_proj_bias,
+                                 void* d_down_proj, void* d_down_proj_bias, void* const* peer_back_w,
+                                 int64_t expert_capacity, int64_t max_rows, int H, int E, int G, int dtype,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_ep(max_rows, H, E, G, 0, dtype);
+  if (rc) return rc;
+  if (!recv_x || !recv_g || !recv_w || !gate_up_proj || !gate_up_proj_bias || !down_proj || !down_proj_bias ||
+      !d_gate_up_proj || !d_gate_up_proj_bias || !d_down_proj || !d_down_proj_bias || !peer_back_w ||
+      expert_capacity < 0)
+    return YAMOE_ERR_BAD_ARG;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < yamoe_b200_ep_backward_workspace_bytes(max_rows, H, E, G, dtype))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  EpPlan p = plan_ep(workspace, max_rows, H, E, G, dtype, true);
+  if (dtype == YAMOE_BF16)
+    return ep_local_backward_impl<__nv_bfloat16>(recv_x, recv_g, recv_w, gate_up_proj, gate_up_proj_bias, down_proj,
+                                                 down_proj_bias, d_gate_up_proj, d_gate_up_proj_bias, d_down_proj,
+                                                 d_down_proj_bias, peer_back_w, expert_capacity, max_rows, H, E / G,
+                                                 G, dtype, p, st);
+  return ep_local_backward_impl<float>(recv_x, recv_g, recv_w, gate_up_proj, gate_up_proj_bias, down_proj,
+                                       down_proj_bias, d_gate_up_proj, d_gate_up_proj_bias, d_down_proj,
+                                       d_down_proj_bias, peer_back_w, expert_capacity, max_rows, H, E / G, G, dtype,
+                                       p, st);
 }
 
 int yamoe_b200_router_topk(const void* router_logits, int64_t* router_indices, void* router_scores, int64_t T, int E,

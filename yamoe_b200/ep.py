@@ -174,7 +174,8 @@ def ep_experts_backward(grad_out, hidden_states, router_indices, routing_weights
 
 
 class PeerExpertParallel:
-    """Expert-parallel forward whose dispatch and combine are peer stores over NVLink.
+    """Expert-parallel forward (and, with `backward=True`, backward) whose dispatch and combine are
+    peer stores over NVLink.
 
     All offsets come from the all-gathered [G, E] count matrix on the device: a call makes no
     device-to-host copy and needs no split sizes.  Buffers that peers write into are symmetric
@@ -189,7 +190,7 @@ class PeerExpertParallel:
     """
 
     def __init__(self, hidden: int, num_experts: int, top_k: int, max_tokens_total: int, max_tokens_local: int,
-                 dtype=torch.bfloat16, group=None, fused_return: bool = False):
+                 dtype=torch.bfloat16, group=None, fused_return: bool = False, backward: bool = False):
         import torch.distributed._symmetric_memory as symm_mem
         self.fused_return = bool(fused_return)
         from . import _lib
@@ -210,9 +211,22 @@ class PeerExpertParallel:
         h_back = symm_mem.rendezvous(self.back, self.group)
         self.peer_recv = torch.tensor(list(h_recv.buffer_ptrs), dtype=torch.int64, device=dev)
         self.peer_back = torch.tensor(list(h_back.buffer_ptrs), dtype=torch.int64, device=dev)
-        self._handles = (h_recv, h_back)
+        self._handles = [h_recv, h_back]
         self.L = _lib.lib()
-        nbytes = self.L.yamoe_b200_ep_workspace_bytes(self.max_rows, self.H, self.E, self.world, self.dt)
+        self.has_backward = bool(backward)
+        if self.has_backward:
+            # upstream-gradient rows and routing weights travel to the expert owners, routing-weight
+            # gradients travel back: three more buffers that peers write into
+            self.recv_g = symm_mem.empty(self.max_rows, self.H, dtype=dtype, device=dev)
+            self.recv_w = symm_mem.empty(self.max_rows, dtype=torch.float32, device=dev)
+            self.back_w = symm_mem.empty(max(self.s_local, 1), dtype=torch.float32, device=dev)
+            hs_ = [symm_mem.rendezvous(t, self.group) for t in (self.recv_g, self.recv_w, self.back_w)]
+            self.peer_recv_g, self.peer_recv_w, self.peer_back_w = (
+                torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=dev) for h in hs_)
+            self._handles += hs_
+        ws_bytes = self.L.yamoe_b200_ep_backward_workspace_bytes if self.has_backward \
+            else self.L.yamoe_b200_ep_workspace_bytes
+        nbytes = ws_bytes(self.max_rows, self.H, self.E, self.world, self.dt)
         if nbytes == 0:
             raise RuntimeError("yamoe_b200: unsupported expert-parallel configuration")
         self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
@@ -220,6 +234,10 @@ class PeerExpertParallel:
         self.counts_all = torch.empty(self.world, self.E, dtype=torch.int32, device=dev)
         self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
         self._check = _lib.check
+        # padding rows of the receive buffer enter the weight-gradient GEMMs as the k dimension
+        # (times zero): they must hold finite values, so start from zeros before any peer writes
+        self.recv.zero_()
+        self._barrier()
 
     def _barrier(self):
         dist.all_reduce(self.flag, group=self.group)      # stream-ordered; orders the peer stores
@@ -253,3 +271,55 @@ class PeerExpertParallel:
                         "ep_return")
         self._barrier()
         return ops.combine_rows(self.back[: T * K], si, router_indices, routing_weights, self.E)
+
+    def backward(self, grad_out, hidden_states, router_indices, routing_weights, gate_up_local, gate_up_bias_local,
+                 down_local, down_bias_local, expert_capacity: int):
+        """Expert-parallel `experts_backward` over the same peer buffers (made with `backward=True`).
+        Returns what `ep_experts_backward` returns: (d_hidden [T_r,H], d_routing [T_r, cols],
+        d_gate_up_local, d_gate_up_bias_local, d_down_local, d_down_bias_local)."""
+        from . import ops
+        if not self.has_backward:
+            raise RuntimeError("PeerExpertParallel: made without backward=True")
+        T, K = router_indices.shape
+        H, E = self.H, self.E
+        if T * K > self.s_local or K != self.K or hidden_states.shape[1] != H:
+            raise RuntimeError("PeerExpertParallel: call exceeds the sizes the buffers were made for")
+        L, st = self.L, torch.cuda.current_stream().cuda_stream
+        dt, dev = hidden_states.dtype, hidden_states.device
+        hs = hidden_states.contiguous()
+        go = grad_out.reshape(T, H).contiguous()
+        rw = routing_weights.contiguous()
+        rcols = rw.shape[1]
+        sv, si, bins, counts = ops.route(router_indices, E)
+        dist.all_gather_into_tensor(self.counts_all.view(-1), counts, group=self.group)
+        ws, S = self.ws.data_ptr(), T * K
+        self._check(L.yamoe_b200_ep_plan(self.counts_all.data_ptr(), self.world, self.rank, E, int(expert_capacity),
+                                         self.peer_back.data_ptr(), self.max_rows, H, self.dt, ws, self.ws.numel(),
+                                         st), "ep_plan")
+        for src, peers in ((hs, self.peer_recv), (go, self.peer_recv_g)):
+            self._check(L.yamoe_b200_ep_dispatch(src.data_ptr(), sv.data_ptr(), si.data_ptr(), bins.data_ptr(), S,
+                                                 peers.data_ptr(), self.max_rows, H, E, self.world, K, self.dt, ws,
+                                                 st), "ep_dispatch")
+        self._check(L.yamoe_b200_ep_dispatch_weights(rw.data_ptr(), rcols, sv.data_ptr(), si.data_ptr(),
+                                                     bins.data_ptr(), S, self.peer_recv_w.data_ptr(), self.max_rows,
+                                                     H, E, self.world, K, self.dt, ws, st), "ep_dispatch_weights")
+        self._barrier()
+        d_wgu, d_bgu = torch.empty_like(gate_up_local), torch.empty_like(gate_up_bias_local)
+        d_wd, d_bd = torch.empty_like(down_local), torch.empty_like(down_bias_local)
+        self._check(L.yamoe_b200_ep_local_backward(
+            self.recv.data_ptr(), self.recv_g.data_ptr(), self.recv_w.data_ptr(), gate_up_local.data_ptr(),
+            gate_up_bias_local.data_ptr(), down_local.data_ptr(), down_bias_local.data_ptr(), d_wgu.data_ptr(),
+            d_bgu.data_ptr(), d_wd.data_ptr(), d_bd.data_ptr(), self.peer_back_w.data_ptr(), int(expert_capacity),
+            self.max_rows, H, E, self.world, self.dt, ws, self.ws.numel(), st), "ep_local_backward")
+        self._barrier()
+        n_sorted = si.numel()
+        ones = torch.ones(T, K, dtype=dt, device=dev)
+        d_hidden = ops.combine_rows(self.back[:S], si, router_indices, ones, E)
+        d_sel = torch.zeros(S, dtype=dt, device=dev)
+        d_sel[si.long()] = self.back_w[:n_sorted].to(dt)
+        if rcols == E:
+            d_routing = torch.zeros(T, E, dtype=dt, device=dev)
+            d_routing.scatter_(1, router_indices.to(torch.int64), d_sel.view(T, K))
+        else:
+            d_routing = d_sel.view(T, K)
+        return d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd
