@@ -55,10 +55,10 @@ def test_batch_mm_fp32():
     orc.check_close(out.cpu(), torch.bmm(x, w), 1e-5, "batch_mm fp32")
 
 
-@pytest.mark.parametrize("switch", ["YAMOE_B200_2CTA", "YAMOE_B200_FUSED_GATHER"])
+@pytest.mark.parametrize("switch", ["YAMOE_B200_2CTA", "YAMOE_B200_FUSED_GATHER", "YAMOE_B200_SWAP"])
 def test_opt_in_kernel_variants_in_subprocess(switch):
-    """The cta_group::2 GEMM and the TMA-gather-fused gate_up GEMM are selected by environment
-    variables read once per process."""
+    """The cta_group::2 GEMM, the TMA-gather-fused gate_up GEMM and the swapped-operand pair GEMM
+    (forward and data gradients) are selected by environment variables read once per process."""
     import os
     import subprocess
     import sys
@@ -79,9 +79,14 @@ def test_opt_in_kernel_variants_in_subprocess(switch):
         "o = yamoe_b200.experts(*[inp[k].cuda() for k in keys], 700, 8, 2)\n"
         "ref = orc.experts_forward_oracle(*[inp[k] for k in keys], 700, 8, 2)\n"
         "orc.check_close(o.float().cpu(), ref, 2e-2, 'two-CTA forward', rel_l2=1e-2)\n"
+        "inp = workloads.make_inputs(300, 128, 4, 2, seed=5, weight_std=0.1, bias_std=0.2, dtype=torch.bfloat16, with_grad=True)\n"
+        "got = yamoe_b200.experts_backward(inp['grad_out'].cuda(), *[inp[k].cuda() for k in keys], 100, 4, 2)\n"
+        "ref = orc.experts_backward_oracle(inp['grad_out'], *[inp[k] for k in keys], 100, 4, 2)\n"
+        "for g, r, n in zip(got, ref, ['d_hidden', 'd_routing', 'd_wgu', 'd_bgu', 'd_wd', 'd_bd']):\n"
+        "    orc.check_close(g.float().cpu(), r, 2e-2, 'variant backward ' + n, rel_l2=2e-2)\n"
         "print('ok')\n")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, PYTHONPATH=root)
-    env[switch] = "1"
+    env[switch] = "2" if switch == "YAMOE_B200_SWAP" else "1"
     res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0 and "ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

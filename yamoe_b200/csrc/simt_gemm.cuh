@@ -29,6 +29,7 @@ struct GemmArgs {
   const int32_t* header;
   const int32_t* pair_expert = nullptr;   // tile-pair tables (256-row tcgen05 kernel only)
   const int32_t* pair_off = nullptr;
+  const int32_t* counts = nullptr;        // rows present per expert (swapped-operand tcgen05 kernel only)
   // tcgen05 kFwd only: A is the UN-permuted source [gather_src_rows, K]; row r of the padded layout
   // is source row gather_rows[r] (negative = padding), fetched by TMA gather
   const int32_t* gather_rows = nullptr;

@@ -320,14 +320,4 @@ inline int launch_umma_gemm_2cta(const GemmArgs& g, const Epi& epi, int64_t max_
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
-// Row-tiled GEMMs go to the two-CTA kernel when it is enabled and the pair tables exist.
-template <int MODE, class Epi>
-inline int launch_umma(const GemmArgs& g, const Epi& epi, int64_t max_rows, int64_t max_tiles, cudaStream_t stream) {
-  if constexpr (MODE != kWgrad) {
-    if (umma_2cta_enabled() && g.pair_expert != nullptr && g.pair_off != nullptr && g.gather_rows == nullptr)
-      return launch_umma_gemm_2cta<MODE>(g, epi, max_rows, max_tiles, stream);
-  }
-  return launch_umma_gemm<MODE>(g, epi, max_rows, max_tiles, stream);
-}
-
 }  // namespace yb

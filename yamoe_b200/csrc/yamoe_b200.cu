@@ -15,6 +15,7 @@
 #include "simt_gemm.cuh"
 #include "umma_gemm.cuh"
 #include "umma_gemm_2cta.cuh"
+#include "umma_gemm_swap.cuh"
 #include "gemv.cuh"
 #include "ep_p2p.cuh"
 #include "router.cuh"
@@ -208,9 +209,9 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
   EpiScatterAdd<T, true, true> comb{reinterpret_cast<const T*>(bd), acc, p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g1{p.xs, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, E,
               p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  g1.pair_expert = p.rt.pair_expert; g1.pair_off = p.rt.pair_off;
+  g1.pair_expert = p.rt.pair_expert; g1.pair_off = p.rt.pair_off; g1.counts = p.rt.counts;
   GemmArgs g2{p.act, H, wd, H, (int64_t)H * H, 0, H, H, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  g2.pair_expert = p.rt.pair_expert; g2.pair_off = p.rt.pair_off;
+  g2.pair_expert = p.rt.pair_expert; g2.pair_off = p.rt.pair_off; g2.counts = p.rt.counts;
   if (fused_gather) {
     g1.A = hidden;
     g1.gather_rows = p.rt.row_token;
@@ -280,9 +281,9 @@ static int forward_train_impl(const void* hidden, const int64_t* ridx, const voi
   EpiWeightedRows<T> wrows{reinterpret_cast<const T*>(bd), yrows, p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g1{p.xs, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, E,
               p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  g1.pair_expert = p.rt.pair_expert; g1.pair_off = p.rt.pair_off;
+  g1.pair_expert = p.rt.pair_expert; g1.pair_off = p.rt.pair_off; g1.counts = p.rt.counts;
   GemmArgs g2{act, H, wd, H, (int64_t)H * H, 0, H, H, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  g2.pair_expert = p.rt.pair_expert; g2.pair_off = p.rt.pair_off;
+  g2.pair_expert = p.rt.pair_expert; g2.pair_off = p.rt.pair_off; g2.counts = p.rt.counts;
   if (use_tcgen05(current_path(), dtype, H)) {
     if constexpr (sizeof(T) == 2) {
       if ((rc = launch_umma<kFwd>(g1, glu, p.max_rows, p.max_tiles, st))) return rc;
@@ -338,25 +339,25 @@ static int backward_impl(const void* grad_out, int per_slot, const void* hidden,
                 reinterpret_cast<T*>(p.pre), p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g1{p.xs, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, E,
               p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  g1.pair_expert = p.rt.pair_expert; g1.pair_off = p.rt.pair_off;
+  g1.pair_expert = p.rt.pair_expert; g1.pair_off = p.rt.pair_off; g1.counts = p.rt.counts;
   // 2. gI' = gys W_d^T; fused GLU backward -> gpre, routing-weight gradient -> gw_row
   EpiGluBackward<T> glub{reinterpret_cast<const T*>(p.pre), reinterpret_cast<T*>(p.gpre), p.gw_row,
                          p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g2{p.gys, H, wd, H, (int64_t)H * H, 0, H, H, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  g2.pair_expert = p.rt.pair_expert; g2.pair_off = p.rt.pair_off;
+  g2.pair_expert = p.rt.pair_expert; g2.pair_off = p.rt.pair_off; g2.counts = p.rt.counts;
   // 3. dW_d[e] = actw_e^T gys_e
   EpiStore<T> st_wd{reinterpret_cast<T*>(d_wd), H, H};
   GemmArgs g3{p.actw, H, p.gys, H, 0, H, H, 0, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  g3.pair_expert = p.rt.pair_expert; g3.pair_off = p.rt.pair_off;
+  g3.pair_expert = p.rt.pair_expert; g3.pair_off = p.rt.pair_off; g3.counts = p.rt.counts;
   // 4. dHidden[token] += gpre W_gu^T
   EpiScatterAdd<T, false, false> sc_dh{nullptr, acc, p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g4{p.gpre, 2 * (int64_t)H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, H, 2 * H, E,
               p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  g4.pair_expert = p.rt.pair_expert; g4.pair_off = p.rt.pair_off;
+  g4.pair_expert = p.rt.pair_expert; g4.pair_off = p.rt.pair_off; g4.counts = p.rt.counts;
   // 5. dW_gu[e] = xs_e^T gpre_e
   EpiStore<T> st_wgu{reinterpret_cast<T*>(d_wgu), H, 2 * H};
   GemmArgs g5{p.xs, H, p.gpre, 2 * (int64_t)H, 0, H, 2 * H, 0, E, p.rt.tile_expert, p.rt.pad_off, p.rt.header};
-  g5.pair_expert = p.rt.pair_expert; g5.pair_off = p.rt.pair_off;
+  g5.pair_expert = p.rt.pair_expert; g5.pair_off = p.rt.pair_off; g5.counts = p.rt.counts;
 
   if (use_tcgen05(path, dtype, H)) {
     if constexpr (sizeof(T) == 2) {
@@ -509,9 +510,9 @@ static int ep_local_forward_impl(const void* recv_x, const void* wgu, const void
   const bool fused = yrows == nullptr;     // results go straight to the source ranks
   GemmArgs g1{recv_x, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, per, rt.tile_expert, rt.pad_off,
               rt.header};
-  g1.pair_expert = rt.pair_expert; g1.pair_off = rt.pair_off;
+  g1.pair_expert = rt.pair_expert; g1.pair_off = rt.pair_off; g1.counts = rt.counts;
   GemmArgs g2{p.act, H, wd, H, (int64_t)H * H, 0, H, H, per, rt.tile_expert, rt.pad_off, rt.header};
-  g2.pair_expert = rt.pair_expert; g2.pair_off = rt.pair_off;
+  g2.pair_expert = rt.pair_expert; g2.pair_off = rt.pair_off; g2.counts = rt.counts;
   int rc = YAMOE_OK;
   if (use_tcgen05(current_path(), dtype, H)) {
     if constexpr (sizeof(T) == 2) {
@@ -548,7 +549,7 @@ static int ep_local_backward_impl(const void* recv_x, const void* recv_g, const 
   gather_grad_kernel<T><<<(unsigned)ceil_div(max_rows, kRowWarps), kRowWarps * 32, 0, st>>>(
       reinterpret_cast<const T*>(recv_g), 1, reinterpret_cast<const T*>(bd), reinterpret_cast<T*>(p.gys), p.gw_row,
       rt.row_token, rt.tile_expert, rt.header, H);
-  auto with_pairs = [&](GemmArgs g) { g.pair_expert = rt.pair_expert; g.pair_off = rt.pair_off; return g; };
+  auto with_pairs = [&](GemmArgs g) { g.pair_expert = rt.pair_expert; g.pair_off = rt.pair_off; g.counts = rt.counts; return g; };
   EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), nullptr, reinterpret_cast<T*>(p.act), reinterpret_cast<T*>(p.pre),
                 rt.row_token, rt.row_weight, H};
   const GemmArgs g1 = with_pairs(GemmArgs{recv_x, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, per,
