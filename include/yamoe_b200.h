@@ -247,6 +247,25 @@ int yamoe_b200_ep_local_backward(const void *recv_x, const void *recv_g, const f
                                  void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The reference's three small sub-operators on its padded [E, C, H] layout.  The expert op of this
+ * library never builds that layout; these are for callers of the standalone operators.
+ *   binned_gather   replaces gather_cuda        (csrc/gather.cu:68-109, torch-ext/torch_binding.cpp:9-17)
+ *                   out[e, i, :] = x[indices[bins[e-1] + i] / top_k, :] for i < min(count_e, C), else 0
+ *   binned_scatter  replaces scatter_cuda       (csrc/scatter.cu:110-147, torch_binding.cpp:19-29)
+ *                   y[tok, :] += weights[bins[e-1] + i] * src[e, i, :]; weights may be NULL (= 1);
+ *                   y is accumulated into, atomically, as in the reference
+ *   index_select    replaces index_select_out_cuda (csrc/index_select.cu:18-52, torch_binding.cpp:44-48)
+ *                   out[i] = in[idx[i]]
+ * indices: int32 [S] flat (token, slot) positions in expert-sorted order; bins: int32 [E] inclusive
+ * prefix sums of the per-expert counts.
+ * ------------------------------------------------------------------------------------------- */
+int yamoe_b200_binned_gather(const void *x, const int32_t *indices, const int32_t *bins, void *out, int64_t T,
+                             int H, int E, int64_t C, int top_k, int dtype, void *stream);
+int yamoe_b200_binned_scatter(const void *src, const int32_t *indices, const int32_t *bins, const void *weights,
+                              void *y, int64_t T, int H, int E, int64_t C, int top_k, int dtype, void *stream);
+int yamoe_b200_index_select(void *out, const void *in, const int32_t *idx, int64_t N, int dtype, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Router tail of the layer that calls the expert op.  Replaces the top-k / softmax / scatter
  * chain of Yamoe.forward (torch-ext/yamoe/layers.py:136-149):
  *   router_indices [T,K] int64  = experts of the K largest logits, descending

@@ -162,6 +162,40 @@ def experts_backward_oracle(grad_out, hidden_states, router_indices, routing_wei
 from yamoe_b200.workloads import make_inputs, make_readme_inputs, make_routing  # noqa: E402,F401
 
 
+def binned_gather_oracle(x, indices, bins, num_experts, capacity, top_k):
+    """out[e, i] = x[indices[bins[e-1] + i] // top_k] for i < min(count_e, capacity), zeros elsewhere
+    (csrc/gather.cu:17-62; torch-ext/yamoe/vendored/yamoe_ref.py:4-15)."""
+    T, H = x.shape
+    out = torch.zeros(num_experts, capacity, H, dtype=x.dtype)
+    for e in range(num_experts):
+        start = int(bins[e - 1]) if e else 0
+        n = min(int(bins[e]) - start, capacity)
+        if n > 0:
+            tok = indices[start:start + n].long() // top_k
+            ok = (tok >= 0) & (tok < T)
+            out[e, :n][ok] = x[tok[ok]]
+    return out
+
+
+def binned_scatter_oracle(src, indices, bins, weights_sorted, y, top_k, compute_dtype=torch.float64):
+    """y[tok] += weights_sorted[bins[e-1] + i] * src[e, i] for i < min(count_e, capacity)
+    (csrc/scatter.cu:67-108).  `weights_sorted` is indexed by sorted position, as in the CUDA
+    operator; yamoe_ref.py:18-35 indexes the un-sorted weights by flat position, which is the same
+    value.  Accumulates in `compute_dtype` and returns a new tensor of y's dtype."""
+    E, C, H = src.shape
+    T = y.shape[0]
+    acc = y.to(compute_dtype).clone()
+    for e in range(E):
+        start = int(bins[e - 1]) if e else 0
+        n = min(int(bins[e]) - start, C)
+        for i in range(n):
+            tok = int(indices[start + i]) // top_k
+            if 0 <= tok < T:
+                w = 1.0 if weights_sorted is None else weights_sorted[start + i].to(compute_dtype)
+                acc[tok] += w * src[e, i].to(compute_dtype)
+    return acc.to(y.dtype)
+
+
 def router_oracle(hidden, router_weight, router_bias, top_k):
     """Router of the layer that feeds the expert op (torch-ext/yamoe/vendored/gpt_oss_mlp.py:127-139,
     torch-ext/yamoe/layers.py:126-149): logits = x W^T + b, top-k on the logits, softmax over the k

@@ -11,7 +11,8 @@ It imports, by file path, the reference's pure-PyTorch implementations
     torch-ext/yamoe/vendored/yamoe_ref.py                       (binned, capacity-aware)
 
 runs them on CPU on seeded inputs, checks that they agree with each other where they
-should, and writes inputs + outputs as .npz files.  The only change made to the imported
+should, and writes inputs + outputs as .npz files (`subops_small.npz`: binned_gather / binned_scatter of
+yamoe_ref.py for the standalone gather / scatter operators).  The only change made to the imported
 code is that `yamoe_ref.sort_tokens_by_expert` is replaced by a version calling
 `torch.sort(stable=True)`: the reference CUDA path sorts with a stable radix sort
 (csrc/sort.cu:30) while yamoe_ref.py:40 uses torch's default sort, which is not stable on
@@ -134,6 +135,26 @@ def main():
                         down_proj_bias=mlp.experts.down_proj_bias.detach().numpy(),
                         dims=np.array([T, H, E, K], dtype=np.int64))
     print("mlp_small ok", out_mlp.abs().max().item())
+
+    # the padded [E, C, H] sub-operators: binned_gather / binned_scatter of yamoe_ref.py
+    T, H, E, K = 37, 24, 6, 3
+    inp = small_inputs(T, H, E, K, 11, with_grad=False)
+    sv, si, counts, bins = orc.route_oracle(inp["router_indices"], E)
+    sub = {}
+    for cap in (T, 5):
+        g = yref.binned_gather(inp["hidden_states"], si, bins[:E], cap, K)
+        gen = torch.Generator().manual_seed(cap)
+        src = torch.randn(E, cap, H, generator=gen)
+        sel = torch.gather(inp["routing_weights"], 1, inp["router_indices"]).reshape(-1)
+        sc = yref.binned_scatter(src, si, sel, bins[:E], cap, K)
+        sc_plain = yref.binned_scatter(src, si, None, bins[:E], cap, K)
+        sub.update({f"gather_c{cap}": g.numpy(), f"src_c{cap}": src.numpy(), f"scatter_c{cap}": sc.numpy(),
+                    f"scatter_plain_c{cap}": sc_plain.numpy()})
+    np.savez_compressed(os.path.join(HERE, "subops_small.npz"), hidden_states=inp["hidden_states"].numpy(),
+                        router_indices=inp["router_indices"].numpy(), routing_weights=inp["routing_weights"].numpy(),
+                        sorted_indices=si.numpy(), bins=bins.numpy(), dims=np.array([T, H, E, K], dtype=np.int64),
+                        **sub)
+    print("subops_small ok")
 
     # README workload digest (full size, fp32, forward only)
     inp = orc.make_readme_inputs(batch=2)

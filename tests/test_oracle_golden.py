@@ -78,3 +78,20 @@ def test_readme_workload_digest():
     assert (out[::16, ::45] - g["sub_train"]).abs().max() <= 1e-4 * scale
     assert (out[::16, ::45] - g["sub_eval"]).abs().max() <= 1e-4 * scale
     assert (out.double().sum(1) - g["rowsum_train"]).abs().max() <= 1e-4 * scale * 54
+
+
+@pytest.mark.parametrize("cap", [37, 5])
+def test_binned_gather_scatter_oracles_match_reference(cap):
+    """binned_gather / binned_scatter of the reference's yamoe_ref.py (full and dropping capacity)."""
+    g = load_golden("subops_small")
+    T, H, E, K = g["dims"].tolist()
+    si, bins = g["sorted_indices"], g["bins"]
+    out = orc.binned_gather_oracle(g["hidden_states"], si, bins, E, cap, K)
+    assert torch.equal(out, g[f"gather_c{cap}"])
+    sel = torch.gather(g["routing_weights"], 1, g["router_indices"]).reshape(-1)
+    w_sorted = sel[si.long()]
+    src = g[f"src_c{cap}"]
+    y = orc.binned_scatter_oracle(src, si, bins, w_sorted, torch.zeros(T, H), K)
+    orc.check_close(y, g[f"scatter_c{cap}"], 1e-6, "binned_scatter")
+    y1 = orc.binned_scatter_oracle(src, si, bins, None, torch.zeros(T, H), K)
+    orc.check_close(y1, g[f"scatter_plain_c{cap}"], 1e-6, "binned_scatter without weights")

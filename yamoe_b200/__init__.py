@@ -2,7 +2,8 @@
 the reference's operator interface (torch-ext/yamoe/__init__.py:6-12)."""
 from . import _lib
 from .layers import Yamoe, _ExpertsFn, experts_autograd
-from .ops import router_topk, batch_mm, batch_mm_wgrad, bincount_cumsum, experts, experts_backward, route, sort
+from .ops import (batch_mm, batch_mm_wgrad, bincount_cumsum, experts, experts_backward, gather, index_select_out,
+                  route, router_topk, scatter, sort)
 
 
 def set_path(name: str) -> str:
@@ -12,5 +13,5 @@ def set_path(name: str) -> str:
     return names[prev]
 
 
-__all__ = ["experts", "experts_backward", "sort", "bincount_cumsum", "route", "batch_mm", "batch_mm_wgrad", "experts_autograd", "Yamoe", "router_topk",
-           "_ExpertsFn", "set_path"]
+__all__ = ["experts", "experts_backward", "sort", "bincount_cumsum", "gather", "scatter", "index_select_out", "route",
+           "batch_mm", "batch_mm_wgrad", "experts_autograd", "Yamoe", "router_topk", "_ExpertsFn", "set_path"]

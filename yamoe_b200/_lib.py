@@ -52,6 +52,11 @@ SIGNATURES = {
                                                c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "yamoe_b200_ep_local_backward": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int, c_int,
                                                                c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_binned_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_int,
+                                         c_int, c_void_p]),
+    "yamoe_b200_binned_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                          c_int64, c_int, c_int, c_void_p]),
+    "yamoe_b200_index_select": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "yamoe_b200_router_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "yamoe_b200_experts_forward_saving": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 5 +
                                           [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),

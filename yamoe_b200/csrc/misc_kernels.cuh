@@ -242,4 +242,86 @@ combine_rows_kernel(const T* __restrict__ rows, const int32_t* __restrict__ inv,
   }
 }
 
+// ---- the reference's three small sub-operators on its padded [E, C, H] layout ------------------
+// This library's own path never materialises [E, C, H]; these serve callers of the standalone ops.
+
+// out[e, i, :] = x[indices[bins[e-1] + i] / top_k, :] for i < min(count_e, C), zeros otherwise.
+// reference: csrc/gather.cu:7-66.  One warp per (e, i); VEC: 16-byte copies.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kRowWarps * 32)
+binned_gather_kernel(const T* __restrict__ x, const int32_t* __restrict__ indices, const int32_t* __restrict__ bins,
+                     T* __restrict__ out, int64_t Tn, int H, int E, int C, int top_k) {
+  const int64_t r = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+  if (r >= (int64_t)E * C) return;
+  const int lane = threadIdx.x & 31;
+  const int e = (int)(r / C), i = (int)(r - (int64_t)e * C);
+  const int start = e ? bins[e - 1] : 0;
+  int64_t tok = -1;
+  if (i < bins[e] - start) {
+    tok = indices[start + i] / top_k;
+    if (tok < 0 || tok >= Tn) tok = -1;
+  }
+  T* dst = out + (size_t)r * H;
+  if constexpr (VEC) {
+    const int nvec = H * (int)sizeof(T) / 16;
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    if (tok < 0) {
+      for (int v = lane; v < nvec; v += 32) d[v] = make_uint4(0, 0, 0, 0);
+    } else {
+      const uint4* sp = reinterpret_cast<const uint4*>(x + (size_t)tok * H);
+      for (int v = lane; v < nvec; v += 32) d[v] = __ldg(sp + v);
+    }
+  } else {
+    for (int h = lane; h < H; h += 32) DT<T>::st(dst + h, tok < 0 ? 0.f : DT<T>::ld(x + (size_t)tok * H + h));
+  }
+}
+
+__device__ __forceinline__ void atomic_add_elem(float* p, float v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add_elem(__nv_bfloat16* p, float v) { atomicAdd(p, __float2bfloat16_rn(v)); }
+
+// y[tok, :] += weights[start + i] * src[e, i, :] for i < min(count_e, C).
+// reference: csrc/scatter.cu:67-108: the product is rounded to the storage type, then added
+// atomically with one rounding per addition; the order of a token's K additions is not fixed
+// there either.  One warp per (e, i).
+template <typename T>
+__global__ void __launch_bounds__(kRowWarps * 32)
+binned_scatter_kernel(const T* __restrict__ src, const int32_t* __restrict__ indices,
+                      const int32_t* __restrict__ bins, const T* __restrict__ weights, T* __restrict__ y,
+                      int64_t Tn, int H, int E, int C, int top_k) {
+  const int64_t r = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+  if (r >= (int64_t)E * C) return;
+  const int lane = threadIdx.x & 31;
+  const int e = (int)(r / C), i = (int)(r - (int64_t)e * C);
+  const int start = e ? bins[e - 1] : 0;
+  if (i >= bins[e] - start) return;
+  const int64_t tok = indices[start + i] / top_k;
+  if (tok < 0 || tok >= Tn) return;
+  const float scale = weights != nullptr ? DT<T>::ld(weights + start + i) : 1.0f;
+  const T* sp = src + (size_t)r * H;
+  T* yp = y + (size_t)tok * H;
+  if constexpr (sizeof(T) == 2) {
+    if ((H & 1) == 0 && (reinterpret_cast<uintptr_t>(yp) & 3) == 0 && (reinterpret_cast<uintptr_t>(sp) & 3) == 0) {
+      for (int h = 2 * lane; h < H; h += 64) {
+        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(sp + h);
+        atomicAdd(reinterpret_cast<__nv_bfloat162*>(yp + h),
+                  __floats2bfloat162_rn(__low2float(v) * scale, __high2float(v) * scale));
+      }
+      return;
+    }
+  }
+  for (int h = lane; h < H; h += 32) {
+    float p = DT<T>::ld(sp + h) * scale;
+    if constexpr (sizeof(T) == 2) p = __bfloat162float(__float2bfloat16_rn(p));
+    atomic_add_elem(yp + h, p);
+  }
+}
+
+// out[i] = in[idx[i]]    reference: csrc/index_select.cu:7-16
+template <typename T>
+__global__ void index_select_kernel(const T* __restrict__ in, const int32_t* __restrict__ idx, T* __restrict__ out,
+                                    int64_t N) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < N) out[i] = in[(int64_t)idx[i]];
+}
+
 }  // namespace yb

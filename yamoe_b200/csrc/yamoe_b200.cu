@@ -8,6 +8,8 @@
 #include <cstring>
 #include <mutex>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "epilogues.cuh"
 #include "misc_kernels.cuh"
@@ -1067,6 +1069,66 @@ int yamoe_b200_experts_backward_saved(const void* grad_out, int grad_out_per_slo
                               gate_up_proj, nullptr, down_proj, down_proj_bias, d_hidden, d_routing, d_gate_up_proj,
                               d_gate_up_proj_bias, d_down_proj, d_down_proj_bias, T, H, E, K, expert_capacity, dtype,
                               saved, st, true);
+}
+
+int yamoe_b200_binned_gather(const void* x, const int32_t* indices, const int32_t* bins, void* out, int64_t T, int H,
+                             int E, int64_t C, int top_k, int dtype, void* stream) {
+  if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
+  if (T < 0 || H <= 0 || E <= 0 || C < 0 || top_k <= 0 || (int64_t)E * C >= ((int64_t)1 << 31) || C >= ((int64_t)1 << 31))
+    return YAMOE_ERR_BAD_ARG;
+  if (C == 0) return YAMOE_OK;
+  if (!x || !indices || !bins || !out) return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t es = dtype == YAMOE_BF16 ? 2 : 4;
+  const bool vec = (H * es) % 16 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const unsigned blocks = (unsigned)ceil_div((int64_t)E * C, kRowWarps);
+  auto launch = [&](auto tag, auto vtag) {
+    using T_ = decltype(tag);
+    binned_gather_kernel<T_, decltype(vtag)::value><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const T_*>(x), indices, bins, reinterpret_cast<T_*>(out), T, H, E, (int)C, top_k);
+  };
+  if (dtype == YAMOE_BF16) {
+    if (vec) launch(__nv_bfloat16{}, std::true_type{}); else launch(__nv_bfloat16{}, std::false_type{});
+  } else {
+    if (vec) launch(float{}, std::true_type{}); else launch(float{}, std::false_type{});
+  }
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+int yamoe_b200_binned_scatter(const void* src, const int32_t* indices, const int32_t* bins, const void* weights,
+                              void* y, int64_t T, int H, int E, int64_t C, int top_k, int dtype, void* stream) {
+  if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
+  if (T < 0 || H <= 0 || E <= 0 || C < 0 || top_k <= 0 || (int64_t)E * C >= ((int64_t)1 << 31) || C >= ((int64_t)1 << 31))
+    return YAMOE_ERR_BAD_ARG;
+  if (C == 0 || T == 0) return YAMOE_OK;
+  if (!src || !indices || !bins || !y) return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned blocks = (unsigned)ceil_div((int64_t)E * C, kRowWarps);
+  if (dtype == YAMOE_BF16)
+    binned_scatter_kernel<__nv_bfloat16><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(src), indices, bins, reinterpret_cast<const __nv_bfloat16*>(weights),
+        reinterpret_cast<__nv_bfloat16*>(y), T, H, E, (int)C, top_k);
+  else
+    binned_scatter_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const float*>(src), indices, bins, reinterpret_cast<const float*>(weights),
+        reinterpret_cast<float*>(y), T, H, E, (int)C, top_k);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+int yamoe_b200_index_select(void* out, const void* in, const int32_t* idx, int64_t N, int dtype, void* stream) {
+  if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
+  if (N < 0) return YAMOE_ERR_BAD_ARG;
+  if (N == 0) return YAMOE_OK;
+  if (!out || !in || !idx) return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned blocks = (unsigned)ceil_div(N, 256);
+  if (dtype == YAMOE_BF16)
+    index_select_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(in), idx,
+                                                               reinterpret_cast<__nv_bfloat16*>(out), N);
+  else
+    index_select_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(in), idx,
+                                                       reinterpret_cast<float*>(out), N);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
 int yamoe_b200_device_status(const void* workspace, void* stream, int32_t* status_out) {

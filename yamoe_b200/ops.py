@@ -1,5 +1,6 @@
-"""torch operators `yamoe_b200::experts` / `experts_backward` / `sort` / `bincount_cumsum`
-with the schemas of the reference binding (torch-ext/torch_binding.cpp:31-42, 58-83),
+"""torch operators `yamoe_b200::experts` / `experts_backward` / `sort` / `bincount_cumsum` /
+`gather` / `scatter` / `index_select_out` / `batch_mm`
+with the schemas of the reference binding (torch-ext/torch_binding.cpp:9-83),
 implemented as thin calls into the C ABI: validate, allocate the output and one workspace
 tensor with torch, pass raw pointers and torch's current stream.
 """
@@ -25,6 +26,12 @@ torch.library.define("yamoe_b200::sort", "(Tensor x, int end_bit, Tensor(a!) x_o
 torch.library.define("yamoe_b200::batch_mm",
                      "(Tensor x, Tensor weights, Tensor batch_sizes, Tensor(a!) output, bool trans_b=False) -> Tensor")
 torch.library.define("yamoe_b200::bincount_cumsum", "(Tensor input, Tensor(a!) output, int minlength) -> ()")
+torch.library.define("yamoe_b200::gather",
+                     "(Tensor x, Tensor indices, Tensor bins, Tensor(a!) output, int E, int C, int top_k) -> ()")
+torch.library.define("yamoe_b200::scatter",
+                     "(Tensor src, Tensor indices, Tensor bins, Tensor weights, Tensor(a!) y, int T, int E, int C, "
+                     "int top_k) -> ()")
+torch.library.define("yamoe_b200::index_select_out", "(Tensor(a!) out, Tensor input, Tensor idx_int32) -> Tensor(a!)")
 
 
 def _require(cond: bool, msg: str) -> None:
@@ -222,6 +229,67 @@ def _bincount_cumsum_cuda(input, output, minlength):
     output[:minlength].copy_(bins[:minlength])
 
 
+def _binned_checks(name, data, indices, bins, E):
+    _require(data.is_cuda and indices.is_cuda and bins.is_cuda, f"{name}: CUDA tensors expected")
+    _require(data.dtype in _DT, f"{name}: float32 or bfloat16 expected, got {data.dtype}")
+    _require(indices.dtype == torch.int32 and bins.dtype == torch.int32, f"{name}: indices and bins must be int32")
+    _require(bins.numel() >= E, f"{name}: bins must hold E cumulative counts")
+    _require(data.is_contiguous() and indices.is_contiguous() and bins.is_contiguous(),
+             f"{name}: contiguous tensors expected")
+
+
+@torch.library.impl("yamoe_b200::gather", "CUDA")
+def _gather_cuda(x, indices, bins, output, E, C, top_k):
+    """reference: csrc/gather.cu:68-109.  output [E, C, H] is overwritten (zeros beyond each count)."""
+    E, C = int(E), int(C)
+    _binned_checks("gather", x, indices, bins, E)
+    _require(x.dim() == 2, "gather: x must be [T, H]")
+    T, H = x.shape
+    _require(tuple(output.shape) == (E, C, H), "Output tensor must have shape [E, C, H]")
+    _require(output.dtype == x.dtype and output.is_cuda and output.is_contiguous(),
+             "gather: output must be a contiguous CUDA tensor of x's dtype")
+    with torch.cuda.device(x.device):
+        st = _lib.lib().yamoe_b200_binned_gather(x.data_ptr(), indices.data_ptr(), bins.data_ptr(), output.data_ptr(),
+                                                 T, H, E, C, int(top_k), _DT[x.dtype], _stream())
+        _lib.check(st, "gather")
+
+
+@torch.library.impl("yamoe_b200::scatter", "CUDA")
+def _scatter_cuda(src, indices, bins, weights, y, T, E, C, top_k):
+    """reference: csrc/scatter.cu:110-147.  y [T, H] is accumulated into; `weights` [S] are in
+    expert-sorted order (an empty tensor means no scaling)."""
+    T, E, C = int(T), int(E), int(C)
+    _binned_checks("scatter", src, indices, bins, E)
+    _require(src.dim() == 3 and src.shape[0] == E and src.shape[1] == C, "scatter: src must be [E, C, H]")
+    H = src.shape[2]
+    _require(y.is_cuda and y.is_contiguous() and y.dtype == src.dtype and y.dim() == 2 and y.shape[0] >= T
+             and y.shape[1] == H, "scatter: y must be a contiguous [T, H] CUDA tensor of src's dtype")
+    w_ptr = None
+    if weights is not None and weights.numel() > 0:
+        _require(weights.is_cuda and weights.dtype == src.dtype and weights.is_contiguous()
+                 and weights.numel() >= indices.numel(), "scatter: weights must be [S] of src's dtype")
+        w_ptr = weights.data_ptr()
+    with torch.cuda.device(src.device):
+        st = _lib.lib().yamoe_b200_binned_scatter(src.data_ptr(), indices.data_ptr(), bins.data_ptr(), w_ptr,
+                                                  y.data_ptr(), T, H, E, C, int(top_k), _DT[src.dtype], _stream())
+        _lib.check(st, "scatter")
+
+
+@torch.library.impl("yamoe_b200::index_select_out", "CUDA")
+def _index_select_out_cuda(out, input, idx_int32):
+    """reference: csrc/index_select.cu:18-52: out[i] = input[idx[i]] over flat, contiguous tensors."""
+    _require(input.is_cuda and idx_int32.is_cuda and out.is_cuda, "cuda only")
+    _require(idx_int32.dtype == torch.int32, "idx must be int32")
+    _require(input.is_contiguous() and idx_int32.is_contiguous() and out.is_contiguous(), "contiguous required")
+    _require(input.dtype in _DT and out.dtype == input.dtype, "index_select_out: float32 or bfloat16 expected")
+    _require(out.numel() >= idx_int32.numel(), "index_select_out: out is too small")
+    with torch.cuda.device(input.device):
+        st = _lib.lib().yamoe_b200_index_select(out.data_ptr(), input.data_ptr(), idx_int32.data_ptr(),
+                                                idx_int32.numel(), _DT[input.dtype], _stream())
+        _lib.check(st, "index_select_out")
+    return out
+
+
 def _batch_mm_raw(x, weights, out, mode):
     E, C = x.shape[0], x.shape[1]
     M = x.shape[2] if mode == 2 else 0
@@ -302,4 +370,7 @@ experts = torch.ops.yamoe_b200.experts
 batch_mm = torch.ops.yamoe_b200.batch_mm
 experts_backward = torch.ops.yamoe_b200.experts_backward
 sort = torch.ops.yamoe_b200.sort
+gather = torch.ops.yamoe_b200.gather
+scatter = torch.ops.yamoe_b200.scatter
+index_select_out = torch.ops.yamoe_b200.index_select_out
 bincount_cumsum = torch.ops.yamoe_b200.bincount_cumsum
