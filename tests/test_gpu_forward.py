@@ -93,3 +93,14 @@ def test_validation_errors():
         yamoe_b200.experts(inp[0], inp[1], inp[2][:, :3], *inp[3:], T, E, K)
     with pytest.raises(RuntimeError, match="must be on CUDA"):
         yamoe_b200.experts(inp[0].cpu(), *inp[1:], T, E, K)
+
+
+@pytest.mark.parametrize("dtype,cos,rel", [(torch.float32, 0.999999, 1e-5), (torch.bfloat16, 0.9999, 1e-2)])
+def test_compare_table_metrics(dtype, cos, rel, capsys):
+    """The metric table of the reference's compare_example.py, op against oracle."""
+    import compare_table
+    r = compare_table.compare(256, 256, 8, 2, dtype, iters=2)
+    compare_table.print_table(r)
+    text = capsys.readouterr().out
+    assert "Cosine Similarity" in text and "Max Abs Diff" in text
+    assert r["cosine"] > cos and r["rel_l2"] < rel
