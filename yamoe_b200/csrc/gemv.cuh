@@ -7,7 +7,9 @@
 //   gemv_kernel<kGateUp>  act[p, j]  = glu(x_t . W_gu[e][:, 2j] + b, x_t . W_gu[e][:, 2j+1] + b);
 //                         also zeroes the fp32 combine buffer and the slab counters for stage two
 //   gemv_kernel<kDown>    out32[t,:] += w_p * (act[p,:] . W_d[e] + b_d[e]); the last CTA to finish a
-//                         column slab (ticket counter, no waiting) rounds that slab to bf16 output
+//                         column slab (ticket counter, no waiting) rounds that slab to bf16 output;
+//                         with few experts hit, 2 or 4 CTAs (gridDim.z) split the reduction
+//                         dimension of a slab and meet in the same fp32 buffer
 // p = t*K + slot is the flat assignment index.  Grid = (touched-expert slot, column slab).  Every
 // CTA rebuilds the (<= 256 entry) routing in shared memory: histogram, ascending list of touched
 // experts, and the stable row list of its own expert, honouring the capacity
@@ -94,7 +96,7 @@ __device__ __forceinline__ void gemv_accumulate(const __nv_bfloat16* __restrict_
 }
 
 template <int STAGE, int NB>
-__global__ void __launch_bounds__(kGemvThreads)
+__global__ void __launch_bounds__(kGemvThreads, 3)
 gemv_kernel(const GemvArgs g) {
   constexpr int LPR = NB / 8, RPW = 32 / LPR, NPART = 8 * RPW;
   extern __shared__ __align__(16) uint8_t gemv_smem[];
@@ -178,19 +180,27 @@ gemv_kernel(const GemvArgs g) {
   const int cg = lane % LPR;
   const int n = n0 + cg * 8;
   const bool col_ok = n < g.N;
-  const __nv_bfloat16* wp = g.W + (size_t)e * g.Kdim * g.N + n;
+  // reduction range of this CTA: gridDim.z CTAs share one (expert, column slab) and meet in out32
+  int k0 = 0, klen = g.Kdim;
+  if (STAGE == kDown && gridDim.z > 1) {          // 32-bit arithmetic, down stage only
+    const unsigned parts = gridDim.z;
+    const unsigned kchunk = (((unsigned)g.Kdim + parts - 1u) / parts + 63u) & ~63u;
+    k0 = (int)min(blockIdx.z * kchunk, (unsigned)g.Kdim);
+    klen = min((int)kchunk, g.Kdim - k0);
+  }
+  const __nv_bfloat16* wp = g.W + ((size_t)e * g.Kdim + k0) * g.N + n;
   const int part = w * RPW + lane / LPR;
 
   for (int r0 = 0; r0 < n_rows; r0 += kGemvMT) {
     const int mt = min(kGemvMT, n_rows - r0);
     // stage the input rows (bf16) in shared memory
-    const int vec_per_row = g.Kdim / 8;
+    const int vec_per_row = klen / 8;
     for (int i = tid; i < mt * vec_per_row; i += kGemvThreads) {
       const int m = i / vec_per_row, c = i - m * vec_per_row;
       const int p = rows[r0 + m];
       const size_t src_row = (STAGE == kGateUp) ? (size_t)(p / g.K) : (size_t)p;
-      reinterpret_cast<uint4*>(xs + (size_t)m * g.Kdim)[c] =
-          __ldg(reinterpret_cast<const uint4*>(g.x + src_row * g.Kdim) + c);
+      reinterpret_cast<uint4*>(xs + (size_t)m * klen)[c] =
+          __ldg(reinterpret_cast<const uint4*>(g.x + src_row * g.Kdim + k0) + c);
     }
     __syncthreads();
     float acc[kGemvMT][8];
@@ -198,10 +208,10 @@ gemv_kernel(const GemvArgs g) {
     for (int m = 0; m < kGemvMT; ++m)
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[m][j] = 0.f;
-    if (mt == 1) gemv_accumulate<NB, 1>(wp, g.N, g.Kdim, xs, col_ok, acc);
-    else if (mt == 2) gemv_accumulate<NB, 2>(wp, g.N, g.Kdim, xs, col_ok, acc);
-    else if (mt == 3) gemv_accumulate<NB, 3>(wp, g.N, g.Kdim, xs, col_ok, acc);
-    else gemv_accumulate<NB, 4>(wp, g.N, g.Kdim, xs, col_ok, acc);
+    if (mt == 1) gemv_accumulate<NB, 1>(wp, g.N, klen, xs, col_ok, acc);
+    else if (mt == 2) gemv_accumulate<NB, 2>(wp, g.N, klen, xs, col_ok, acc);
+    else if (mt == 3) gemv_accumulate<NB, 3>(wp, g.N, klen, xs, col_ok, acc);
+    else gemv_accumulate<NB, 4>(wp, g.N, klen, xs, col_ok, acc);
     // partial sums -> shared memory: red[part][m][col]
     for (int m = 0; m < mt; ++m) {
       float* dst = red + ((size_t)part * kGemvMT + m) * NB + cg * 8;
@@ -234,7 +244,7 @@ gemv_kernel(const GemvArgs g) {
         float s = 0.f;
 #pragma unroll 4
         for (int pp = 0; pp < NPART; ++pp) s += red[((size_t)pp * kGemvMT + m) * NB + j];
-        s += __bfloat162float(g.bias[(size_t)e * g.N + col]);
+        if (blockIdx.z == 0) s += __bfloat162float(g.bias[(size_t)e * g.N + col]);
         const int p = rows[r0 + m];
         const int t = p / g.K;
         const int wc = (g.routing_cols == g.E) ? e : (p - t * g.K);
@@ -249,7 +259,7 @@ gemv_kernel(const GemvArgs g) {
     __shared__ int s_last;
     __threadfence();
     __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(g.slab_done + blockIdx.y, 1) == s_touched - 1);
+    if (tid == 0) s_last = (atomicAdd(g.slab_done + blockIdx.y, 1) == s_touched * (int)gridDim.z - 1);
     __syncthreads();
     if (s_last) {
       __threadfence();
@@ -276,13 +286,28 @@ inline int gemv_gate_up_slab(int64_t S, int E, int N) {
   return slots * ceil_div(N, 128) < 4 * 148 ? 64 : 128;
 }
 
+// Number of CTAs that share the reduction dimension of one (expert, column slab) in the down
+// stage.  With few experts hit, one CTA per slab leaves the grid (slots x 45 slabs) too coarse to
+// balance over 148 SMs: 180 CTAs at T = 1 put two slabs on some SMs and one on others.
+// YAMOE_B200_GEMV_KS overrides (1, 2 or 4).
+inline int gemv_down_ksplit(int64_t S, int E, int N) {
+  static int forced = []() {
+    const char* env = std::getenv("YAMOE_B200_GEMV_KS");
+    const int v = env ? std::atoi(env) : 0;
+    return (v == 1 || v == 2 || v == 4) ? v : 0;
+  }();
+  if (forced) return forced;
+  const int64_t ctas = (E < S ? E : S) * ceil_div(N, 64);
+  return ctas <= 2 * 148 ? 2 : 1;     // measured: 53.6 / 55.0 / 55.6 us with 2 / 1 / 4 parts at T = 1; no gain beyond
+}
+
 inline bool gemv_preferred(int64_t T, int E, int K) {
   const int64_t S = T * K;
   return S <= kGemvMaxS && S <= 4 * (int64_t)E;   // at most ~4 rows per expert on average
 }
 
 template <int STAGE, int NB>
-inline int launch_gemv_stage(const GemvArgs& g, cudaStream_t st) {
+inline int launch_gemv_stage(const GemvArgs& g, cudaStream_t st, int ksplit = 1) {
   constexpr int NPART = 8 * (32 / (NB / 8));
   size_t smem = (((size_t)kGemvMT * g.Kdim * 2 + 15) & ~size_t(15)) + (size_t)NPART * kGemvMT * NB * 4 +
                 (size_t)g.E * 4 + 2 * kGemvMaxS * 4;
@@ -294,7 +319,7 @@ inline int launch_gemv_stage(const GemvArgs& g, cudaStream_t st) {
     configured = smem;
   }
   const int slots = g.E < g.S ? g.E : g.S;
-  dim3 grid((unsigned)slots, (unsigned)ceil_div(g.N, NB));
+  dim3 grid((unsigned)slots, (unsigned)ceil_div(g.N, NB), (unsigned)(STAGE == kDown ? ksplit : 1));
   if (STAGE == kDown) {
     if (launch_pdl(kern, grid, dim3(kGemvThreads), smem, st, g) != cudaSuccess) return YAMOE_ERR_CUDA;
   } else {
@@ -326,7 +351,7 @@ inline int launch_gemv_forward(const void* hidden, const int64_t* ridx, const vo
   if (rc) return rc;
   {
     StageTimer tm(kStageDown, st);
-    rc = launch_gemv_stage<kDown, 64>(g2, st);
+    rc = launch_gemv_stage<kDown, 64>(g2, st, gemv_down_ksplit(S, E, H));
   }
   return rc;
 }
