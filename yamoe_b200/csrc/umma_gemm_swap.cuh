@@ -23,7 +23,7 @@
 // functor as zeros (every functor zero-fills or skips padding rows).
 //
 // Roles, signals across the pair, bounded waits and the abort path are those of
-// umma_gemm_2cta.cuh; no TMA multicast is used.
+// umma_gemm_2cta.cuh; every CTA loads its own operands.
 #pragma once
 #include "umma_gemm_2cta.cuh"
 
