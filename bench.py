@@ -445,6 +445,16 @@ def run_ours(args):
                                 "peak_source": peaks["source"] + " (copy bandwidth)",
                                 "frac_of_nominal_8000": achieved / 8000.0, "distinct_experts": distinct,
                                 "whole_op_gbs": distinct * 49783680 / (ms_step * 1e-3) / 1e9}
+        elif gemm_ms and dtype == torch.float32:
+            # fp32 runs on the CUDA cores (FFMA): no measured peak exists for that pipe, so the
+            # fraction is against the nominal 148 SMs x 128 FMA x 2 x 1.965 GHz
+            mean_ms = sum(gemm_ms) / len(gemm_ms)
+            achieved = 4.0 * S * H * H / (mean_ms * 1e-3) / 1e12
+            ffma_peak = 148 * 128 * 2 * 1.965e9 / 1e12
+            line["roofline"] = {"bound": "tensor", "kernel": "simt_gemm_kernel<gate_up + bias + clamped SwiGLU> (fp32 FFMA)",
+                                "achieved": achieved, "peak": ffma_peak, "unit": "TFLOP/s", "frac": achieved / ffma_peak,
+                                "traffic": None, "kernel_ms": mean_ms,
+                                "peak_source": "nominal fp32 FFMA rate (CUDA cores; the tensor pipe is not used in fp32)"}
         elif gemm_ms:
             mean_ms = sum(gemm_ms) / len(gemm_ms)
             achieved = 4.0 * S * H * H / (mean_ms * 1e-3) / 1e12
