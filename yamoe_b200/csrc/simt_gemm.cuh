@@ -8,7 +8,7 @@
 //           reference: csrc/experts_backward.cu:278-280, :309-310
 //   kWgrad  C[e][m, n] = sum_{rows r of expert e} A[r, m] * B[r, n]
 //           reference: csrc/experts_backward.cu:281-282, :311
-// 64x64 output tile, 16-deep k slices, 256 threads, 4x4 accumulators per thread.
+// 128x128 or 64x128 output tile, 16-deep k slices, 256 threads, 8x8 or 4x8 accumulators per thread.
 #pragma once
 #include "common.cuh"
 #include "epilogues.cuh"
@@ -36,91 +36,156 @@ struct GemmArgs {
   int64_t gather_src_rows = 0;
 };
 
-constexpr int kSimtBM = 64, kSimtBN = 64, kSimtBK = 16, kSimtThreads = 256;
+constexpr int kSimtBN = 128, kSimtBK = 16, kSimtThreads = 256;
 
-template <typename T, int MODE, class Epi>
-__global__ void __launch_bounds__(kSimtThreads)
+// NL consecutive elements of a row as fp32 (16-byte loads when `vec`); zeros when `ok` is false.
+// `p` must be 16-byte aligned when `vec` is set.
+template <typename T, int NL>
+__device__ __forceinline__ void simt_load(const T* __restrict__ p, bool ok, bool vec, float (&v)[NL]) {
+  if (!ok) {
+#pragma unroll
+    for (int i = 0; i < NL; ++i) v[i] = 0.f;
+  } else if (vec) {
+    load_vec<T, NL>(p, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < NL; ++i) v[i] = DT<T>::ld(p + i);
+  }
+}
+
+// BM x 128 x 16 tiles (BM = 128 or 64), 256 threads, (BM/16) x 8 accumulators per thread in 4-wide
+// groups 64 apart, so shared-memory reads are conflict-free 16-byte loads; the next k-tile is fetched
+// into registers while the current one is multiplied (two shared-memory buffers, one barrier per
+// k-tile).  BM = 64 is for problems with few rows per expert: a 64-row tile that lies entirely in
+// an expert's padding skips its main loop.  K, N and the row strides are multiples of 8 on every
+// path that reaches this kernel.
+template <typename T, int MODE, int BM, class Epi>
+__global__ void __launch_bounds__(kSimtThreads, 2)
 simt_gemm_kernel(GemmArgs g, Epi epi) {
-  __shared__ __align__(16) float As[kSimtBK][kSimtBM + 4];
-  __shared__ __align__(16) float Bs[kSimtBK][kSimtBN + 4];
+  constexpr int RT = BM / 16;              // rows per thread = elements of A fetched per thread
+  __shared__ __align__(16) float As[2][kSimtBK][BM + 4];
+  __shared__ __align__(16) float Bs[2][kSimtBK][kSimtBN + 4];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int n0 = blockIdx.x * kSimtBN;
   int e, row0, k_begin, k_end, m_limit;
   if constexpr (MODE == kWgrad) {
     e = blockIdx.z;
-    row0 = blockIdx.y * kSimtBM;            // m0 within the expert's output
+    row0 = blockIdx.y * BM;                 // m0 within the expert's output
     k_begin = g.pad_off[e];
     k_end = g.pad_off[e + 1];
     m_limit = g.M;
   } else {
-    row0 = blockIdx.y * kSimtBM;            // padded row
+    row0 = blockIdx.y * BM;                 // padded row
     if (row0 >= g.header[kHdrRowsUsed]) return;
     e = g.tile_expert[row0 / kTileM];
     k_begin = 0;
     k_end = g.K;
-    m_limit = row0 + kSimtBM;
+    m_limit = row0 + BM;
+    if (g.counts != nullptr) {              // nothing but padding in this tile: zeros, no main loop
+      const int begin = g.pad_off[e];
+      const int have = min(g.counts[e], g.pad_off[e + 1] - begin);
+      if (row0 - begin >= have) k_end = 0;
+    }
   }
   const T* __restrict__ A = reinterpret_cast<const T*>(g.A);
   const T* __restrict__ B = reinterpret_cast<const T*>(g.B) + (MODE == kWgrad ? 0 : (size_t)e * g.b_expert_stride);
-  float acc[4][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  constexpr int kAlign = 16 / (int)sizeof(T);
+  const bool vec_a = (g.lda % kAlign) == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && RT % kAlign == 0;
+  const bool vec_b = (g.ldb % kAlign) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0;
 
-  for (int k0 = k_begin; k0 < k_end; k0 += kSimtBK) {
-    // ---- A tile -> As[k][m]
+  // which elements of each operand tile this thread fetches
+  //   A contiguous along k (rows x k):  RT elements at row tid / (16/RT), k offset (tid % (16/RT)) * RT
+  //   A contiguous along m (wgrad):     RT elements at k = tid / 16, m offset (tid % 16) * RT
+  //   B contiguous along k (dgrad):     8 elements at n = tid / 2, k offset (tid % 2) * 8
+  //   B contiguous along n:             8 elements at k = tid / 16, n offset (tid % 16) * 8
+  constexpr int TPR = 16 / RT;
+  const int ak_row = tid / TPR, ak_k = (tid % TPR) * RT;
+  const int am_k = tid >> 4, am_m = (tid & 15) * RT;
+  const int bk_n = tid >> 1, bk_k = (tid & 1) * 8;
+  const int bn_k = tid >> 4, bn_n = (tid & 15) * 8;
+  float ra[RT], rb[8];
+  auto fetch = [&](int k0) {
     if constexpr (MODE == kWgrad) {
-      const int k = tid >> 4, mq = (tid & 15) * 4;
-      const bool kin = (k0 + k) < k_end;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int m = row0 + mq + i;
-        As[k][mq + i] = (kin && m < m_limit) ? DT<T>::ld(A + (size_t)(k0 + k) * g.lda + m) : 0.f;
-      }
+      const int k = k0 + am_k, m = row0 + am_m;
+      simt_load<T, RT>(A + (size_t)k * g.lda + m, k < k_end && m < m_limit, vec_a, ra);
     } else {
-      const int m = tid >> 2, kq = (tid & 3) * 4;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int k = k0 + kq + i;
-        As[kq + i][m] = (k < k_end) ? DT<T>::ld(A + (size_t)(row0 + m) * g.lda + k) : 0.f;
-      }
+      const int k = k0 + ak_k;
+      simt_load<T, RT>(A + (size_t)(row0 + ak_row) * g.lda + k, k < k_end, vec_a, ra);
     }
-    // ---- B tile -> Bs[k][n]
     if constexpr (MODE == kDgrad) {
-      const int n = tid >> 2, kq = (tid & 3) * 4;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int k = k0 + kq + i;
-        Bs[kq + i][n] = (k < k_end && (n0 + n) < g.N) ? DT<T>::ld(B + (size_t)(n0 + n) * g.ldb + k) : 0.f;
-      }
+      const int k = k0 + bk_k, n = n0 + bk_n;
+      simt_load<T, 8>(B + (size_t)n * g.ldb + k, k < k_end && n < g.N, vec_b, rb);
     } else {
-      const int k = tid >> 4, nq = (tid & 15) * 4;
-      const bool kin = (k0 + k) < k_end;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int n = n0 + nq + i;
-        Bs[k][nq + i] = (kin && n < g.N) ? DT<T>::ld(B + (size_t)(k0 + k) * g.ldb + n) : 0.f;
-      }
+      const int k = k0 + bn_k, n = n0 + bn_n;
+      simt_load<T, 8>(B + (size_t)k * g.ldb + n, k < k_end && n < g.N, vec_b, rb);
     }
-    __syncthreads();
+  };
+  auto stage = [&](int buf) {
+    if constexpr (MODE == kWgrad) {
+#pragma unroll
+      for (int i = 0; i < RT; i += 4)
+        *reinterpret_cast<float4*>(&As[buf][am_k][am_m + i]) = make_float4(ra[i], ra[i + 1], ra[i + 2], ra[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < RT; ++i) As[buf][ak_k + i][ak_row] = ra[i];
+    }
+    if constexpr (MODE == kDgrad) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) Bs[buf][bk_k + i][bk_n] = rb[i];
+    } else {
+      *reinterpret_cast<float4*>(&Bs[buf][bn_k][bn_n]) = make_float4(rb[0], rb[1], rb[2], rb[3]);
+      *reinterpret_cast<float4*>(&Bs[buf][bn_k][bn_n + 4]) = make_float4(rb[4], rb[5], rb[6], rb[7]);
+    }
+  };
+
+  float acc[RT][8];
+#pragma unroll
+  for (int i = 0; i < RT; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  int buf = 0;
+  if (k_begin < k_end) {
+    fetch(k_begin);
+    stage(0);
+  }
+  __syncthreads();
+  for (int k0 = k_begin; k0 < k_end; k0 += kSimtBK) {
+    const bool more = k0 + kSimtBK < k_end;
+    if (more) fetch(k0 + kSimtBK);
 #pragma unroll
     for (int kk = 0; kk < kSimtBK; ++kk) {
-      const float4 a4 = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
-      const float4 b4 = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
-      const float a[4] = {a4.x, a4.y, a4.z, a4.w};
-      const float b[4] = {b4.x, b4.y, b4.z, b4.w};
+      float a[RT], b[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int h = 0; h < RT / 4; ++h) {
+        const float4 q = *reinterpret_cast<const float4*>(&As[buf][kk][h * 64 + ty * 4]);
+        a[4 * h] = q.x; a[4 * h + 1] = q.y; a[4 * h + 2] = q.z; a[4 * h + 3] = q.w;
+      }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+      for (int h = 0; h < 2; ++h) {
+        const float4 q = *reinterpret_cast<const float4*>(&Bs[buf][kk][h * 64 + tx * 4]);
+        b[4 * h] = q.x; b[4 * h + 1] = q.y; b[4 * h + 2] = q.z; b[4 * h + 3] = q.w;
+      }
+#pragma unroll
+      for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
     }
+    if (more) stage(buf ^ 1);
     __syncthreads();
+    buf ^= 1;
   }
-  const int n = n0 + tx * 4;
-  if (n >= g.N) return;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) epi.template apply<4>(e, row0 + ty * 4 + i, n, acc[i]);
+  for (int i = 0; i < RT; ++i) {
+    const int row = row0 + (i >> 2) * 64 + ty * 4 + (i & 3);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int n = n0 + h * 64 + tx * 4;
+      if (n >= g.N) continue;
+      const float v[4] = {acc[i][4 * h], acc[i][4 * h + 1], acc[i][4 * h + 2], acc[i][4 * h + 3]};
+      epi.template apply<4>(e, row, n, v);
+    }
+  }
 }
 
 template <typename T, int MODE, class Epi>
@@ -128,13 +193,20 @@ inline void launch_simt_gemm(const GemmArgs& g, const Epi& epi, int64_t max_rows
   dim3 grid;
   grid.x = (unsigned)ceil_div(g.N, kSimtBN);
   if (MODE == kWgrad) {
-    grid.y = (unsigned)ceil_div(g.M, kSimtBM);
+    grid.y = (unsigned)ceil_div(g.M, 128);
     grid.z = (unsigned)g.E;
-  } else {
-    grid.y = (unsigned)ceil_div(max_rows, kSimtBM);
-    grid.z = 1;
+    simt_gemm_kernel<T, MODE, 128, Epi><<<grid, kSimtThreads, 0, stream>>>(g, epi);
+    return;
   }
-  simt_gemm_kernel<T, MODE, Epi><<<grid, kSimtThreads, 0, stream>>>(g, epi);
+  grid.z = 1;
+  // few rows per expert (the padded bound max_rows includes 128 spare rows per expert): 64-row tiles
+  if (g.counts != nullptr && max_rows < (int64_t)640 * g.E) {
+    grid.y = (unsigned)ceil_div(max_rows, 64);
+    simt_gemm_kernel<T, MODE, 64, Epi><<<grid, kSimtThreads, 0, stream>>>(g, epi);
+  } else {
+    grid.y = (unsigned)ceil_div(max_rows, 128);
+    simt_gemm_kernel<T, MODE, 128, Epi><<<grid, kSimtThreads, 0, stream>>>(g, epi);
+  }
 }
 
 }  // namespace yb
