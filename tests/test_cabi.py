@@ -1,6 +1,5 @@
 """The C-ABI library loads and exports every symbol include/yamoe_b200.h declares; argument
 checks that need no GPU."""
-import ctypes
 import os
 import re
 

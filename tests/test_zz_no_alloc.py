@@ -10,7 +10,6 @@ proves the per-call clearing), and that an oversized request is refused without 
 The file name sorts last on purpose: a run that stops at the first failure has then already
 executed every other test.
 """
-import ctypes
 
 import pytest
 import torch
