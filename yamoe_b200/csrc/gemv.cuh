@@ -351,7 +351,15 @@ inline int launch_gemv_forward(const void* hidden, const int64_t* ridx, const vo
   if (rc) return rc;
   {
     StageTimer tm(kStageDown, st);
-    rc = launch_gemv_stage<kDown, 64>(g2, st, gemv_down_ksplit(S, E, H));
+    static const int down_nb = []() {
+      const char* env = std::getenv("YAMOE_B200_GEMV_DOWN_NB");
+      return env ? std::atoi(env) : 0;
+    }();
+    // 128-column slabs pay only when they still give every SM about eight CTAs (T = 64: 1006 us
+    // against 1018 us; T = 16: 465 us against 457 us)
+    const bool wide = down_nb ? down_nb == 128 : (E < S ? E : S) * ceil_div(H, 128) >= 8 * 148;
+    rc = wide ? launch_gemv_stage<kDown, 128>(g2, st, 1)
+              : launch_gemv_stage<kDown, 64>(g2, st, gemv_down_ksplit(S, E, H));
   }
   return rc;
 }
