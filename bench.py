@@ -198,6 +198,58 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def place_near_gpu(local_rank):
+    """Pins this process to the CPUs of the GPU's NUMA node (when the allowed CPU set holds any), so
+    that the pinned host buffers allocated afterwards are local to the GPU's PCIe root.  Returns a
+    small record for the JSON line.  Host-to-device copies from the far socket run at about half
+    the rate."""
+    info = {"numa_node": None, "cpus_before": len(os.sched_getaffinity(0)), "cpus_after": None}
+    info["_allowed"] = os.sched_getaffinity(0)
+    try:
+        import torch
+        props = torch.cuda.get_device_properties(local_rank)
+        if hasattr(props, "pci_bus_id"):
+            bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        else:
+            import pynvml
+            pynvml.nvmlInit()
+            bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(local_rank)).busId
+            bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+            if len(bus.split(":")[0]) == 8:
+                bus = bus[4:]
+        base = f"/sys/bus/pci/devices/{bus}/"
+        info["numa_node"] = int(open(base + "numa_node").read())
+        local = set()
+        for part in open(base + "local_cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            local.update(range(int(lo), int(hi or lo) + 1))
+        want = local & os.sched_getaffinity(0)
+        if want:
+            os.sched_setaffinity(0, want)
+    except Exception as exc:   # no NVML, no sysfs, odd bus id: leave the placement alone
+        info["note"] = type(exc).__name__
+    info["cpus_after"] = len(os.sched_getaffinity(0))
+    return info
+
+
+def copy_bandwidth(torch, nbytes=64 << 20):
+    """Pinned host <-> device copy rates (GB/s), each direction alone: context for `e2e`."""
+    h = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    out = {}
+    for name, fn in (("h2d_gbs", lambda: d.copy_(h, non_blocking=True)), ("d2h_gbs", lambda: h.copy_(d, non_blocking=True))):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(5):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = round(5 * nbytes / (a.elapsed_time(b) * 1e-3) / 1e9, 1)
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -210,6 +262,8 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device; yamoe_b200 has no CPU fallback")
     torch.cuda.set_device(local_rank)
+    host_place = place_near_gpu(local_rank)
+    allowed_cpus = host_place.pop("_allowed")
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
@@ -430,7 +484,8 @@ def run_ours(args):
                               else f"expert weights ({weight_bytes / 1e9:.1f} GB) exceed the 126 MB L2; no flush")},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "pipeline": ("host->device copy, op and device->host copy of consecutive steps overlap on three streams"
-                                 if pipelined else "one stream, copies and op in sequence")},
+                                 if pipelined else "one stream, copies and op in sequence"),
+                    "host": dict(host_place, **copy_bandwidth(torch))},
             "gpu_launches": args.steps * (2 if decode else {"fwd": 6, "bwd": 14, "train": 20}[w["mode"]]),
             "clocks": clocks,
             "achieved_tflops_whole_op": {"fwd": 6, "bwd": 16, "train": 22}[w["mode"]] * S * H * H / (ms_step * 1e-3) / 1e12,
@@ -465,6 +520,7 @@ def run_ours(args):
                                 "kernel_ms": mean_ms, "peak_source": peaks["source"] + " (burst bf16 matmul)",
                                 "frac_of_nominal_2250": achieved / 2250.0}
         if world == 1 and not args.no_cpu_baseline:
+            os.sched_setaffinity(0, allowed_cpus)      # the CPU baseline may use every core again
             v, cores, sample = cpu_reference_time(w, {k: t.cpu() for k, t in inp.items()}, dtype)
             line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
