@@ -81,19 +81,25 @@ __device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Off by default: measured on B200 it did not help (forward 0.843 ms with, 0.814 ms without;
-// decode T=1 66.4 us with, 65.0 us without).  YAMOE_B200_PDL=1 enables it.
-inline bool pdl_enabled() {
-  static int on = []() {
+// Measured on B200: between the two decode GEMV kernels it saves about 2 us per call (T = 1: 52.0 us
+// against 53.8 us as a CUDA-graph replay), so that pair uses it by default; between the kernels of
+// the grouped-GEMM forward it did not help (0.843 ms with, 0.814 ms without) and stays off.
+// YAMOE_B200_PDL=1 turns it on everywhere, YAMOE_B200_PDL=0 off everywhere.
+inline int pdl_setting() {
+  static int v = []() {
     const char* env = std::getenv("YAMOE_B200_PDL");
-    return env ? std::atoi(env) : 0;
+    return env ? (std::atoi(env) != 0 ? 1 : 0) : -1;
   }();
-  return on != 0;
+  return v;
+}
+inline bool pdl_enabled(bool default_on = false) {
+  const int v = pdl_setting();
+  return v < 0 ? default_on : v != 0;
 }
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                              Args&&... args) {
+inline cudaError_t launch_pdl_opt(bool default_on, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t st, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -101,10 +107,16 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled(default_on) ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  return launch_pdl_opt(false, kern, grid, block, smem, st, std::forward<Args>(args)...);
 }
 
 // Routing tables kept at the head of every workspace (all int32 unless noted).

@@ -321,7 +321,7 @@ inline int launch_gemv_stage(const GemvArgs& g, cudaStream_t st, int ksplit = 1)
   const int slots = g.E < g.S ? g.E : g.S;
   dim3 grid((unsigned)slots, (unsigned)ceil_div(g.N, NB), (unsigned)(STAGE == kDown ? ksplit : 1));
   if (STAGE == kDown) {
-    if (launch_pdl(kern, grid, dim3(kGemvThreads), smem, st, g) != cudaSuccess) return YAMOE_ERR_CUDA;
+    if (launch_pdl_opt(true, kern, grid, dim3(kGemvThreads), smem, st, g) != cudaSuccess) return YAMOE_ERR_CUDA;
   } else {
     kern<<<grid, kGemvThreads, smem, st>>>(g);
   }
