@@ -113,6 +113,23 @@ def main():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **save)
         print(name, "ok", out_train.abs().max().item())
 
+    # gradients under a dropping capacity: autograd through binned_experts_ref (stable sort)
+    drop = {}
+    for name, T, H, E, K, seed in cases:
+        inp = small_inputs(T, H, E, K, seed)
+        cap_small = max(1, (T * K) // (2 * E))
+        leaves = {k: inp[k].clone().requires_grad_(True) for k in
+                  ("hidden_states", "routing_weights", "gate_up_proj", "gate_up_proj_bias", "down_proj", "down_proj_bias")}
+        out = yref.binned_experts_ref(leaves["hidden_states"].view(1, T, H), inp["router_indices"],
+                                      leaves["routing_weights"], leaves["gate_up_proj"], leaves["gate_up_proj_bias"],
+                                      leaves["down_proj"], leaves["down_proj_bias"], cap_small).view(T, H)
+        (out * inp["grad_out"]).sum().backward()
+        for key, leaf in zip(("d_hidden", "d_routing", "d_wgu", "d_bgu", "d_wd", "d_bd"), leaves.values()):
+            drop[f"{name}_{key}"] = leaf.grad.numpy()
+        drop[f"{name}_cap"] = np.int64(cap_small)
+    np.savez_compressed(os.path.join(HERE, "drop_grads.npz"), **drop)
+    print("drop_grads ok")
+
     # whole layer (router + experts) from the vendored GptOssMLP
     T, H, E, K = 48, 32, 8, 2
     cfg = types.SimpleNamespace(intermediate_size=H, num_local_experts=E, hidden_size=H, num_experts_per_tok=K)

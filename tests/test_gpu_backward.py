@@ -30,6 +30,16 @@ def test_backward_fp32_golden(name):
         orc.check_close(got, g[key], RTOL_F32, key)
 
 
+@pytest.mark.parametrize("name", SMALL_CASES)
+def test_backward_fp32_golden_dropping_capacity(name):
+    """Against autograd through the reference's binned_experts_ref with a capacity that drops rows."""
+    g, d = load_golden(name), load_golden("drop_grads")
+    T, H, E, K = g["dims"].tolist()
+    grads = run_backward(g["grad_out"], golden_inputs(g), int(d[f"{name}_cap"]), E, K)
+    for got, key in zip(grads, GRADS):
+        orc.check_close(got, d[f"{name}_{key}"], RTOL_F32, key + " (dropping capacity)")
+
+
 def test_backward_capacity_drop_and_slot_shapes():
     g = load_golden("small_c")
     T, H, E, K = g["dims"].tolist()
