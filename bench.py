@@ -15,12 +15,19 @@ softmax/top-4 routing without renormalisation).
                weights are model state and stay resident.
 * `roofline`   gate_up grouped GEMM (the dominant kernel): algorithmic 4*S*H^2 FLOP per launch
                divided by its mean device time, bracketed by CUDA events inside each timed step.
-* `cpu_baseline`  the CPU port of the reference's PyTorch implementation, timed on this box's host
-               cores on a bounded sample (rank 0, N=1 only).
-* `--impl reference`  times that CPU implementation with all host threads on the same workload.
+* `cpu_baseline`  the CPU implementation of the reference's PyTorch experts, timed on this box's
+               host cores on a bounded sample (rank 0, N=1 only).
+* `extra`      N = 1: the decode workloads (T = 1, 4, 16, 64 at the 120B shape) and the backward
+               workload (T = 8192), each with its own clock samples.  N > 1: the strong-scaling
+               expert-parallel workloads (forward and backward at T = 8192, the skewed 120B prefill)
+               for the peer-store and the NCCL all-to-all exchange.
+* `--impl reference`  times the CPU implementation with all host threads on the same workload.
 
-With N > 1 (torchrun) every rank runs the same workload on its own tokens with a full replica of
-the experts: tokens are independent units, so there is no data-path collective (weak scaling).
+With N > 1 (torchrun) the default workload runs EXPERT-PARALLEL and weak-scaled: every rank owns
+4096 tokens (global T = 4096 * N), the 32 experts are sharded contiguously E/N per rank, and
+token rows travel to the expert owners and back over NVLink (`yamoe_b200.ep.PeerExpertParallel`).
+Before the timed loop every rank checks its expert-parallel output against the single-GPU op run
+on the same tokens with all experts (`ep_check`); a failed check makes the run exit non-zero.
 """
 from __future__ import annotations
 
@@ -38,6 +45,7 @@ if ROOT not in sys.path:
 
 KEYS = ["hidden_states", "router_indices", "routing_weights", "gate_up_proj", "gate_up_proj_bias",
         "down_proj", "down_proj_bias"]
+DEFAULT = "gptoss20b_fwd_t4096"
 
 WORKLOADS = {
     # name: (T, H, E, K, mode)
@@ -56,6 +64,16 @@ WORKLOADS = {
     "gptoss20b_train_saved_t8192": dict(T=8192, H=2880, E=32, K=4, mode="train", saved=True),
     "readme_fp32_t512": dict(T=512, H=2880, E=8, K=2, mode="fwd", fp32=True),
 }
+
+# DRAM bytes (read + write) of one launch of the dominant kernel, from ncu captures of that kernel;
+# keyed by workload and output-tile width.  The source names the summary that holds the capture.
+TRAFFIC = {
+    ("gptoss20b_fwd_t4096", 256): (1.268e9, "ncu dram__bytes_read.sum + dram__bytes_write.sum of one gate_up launch, "
+                                            "profiles/umma_gemm_gptoss20b_fwd_t4096.md"),
+}
+
+# kernels of this library launched by one call (memsets not counted)
+LAUNCHES = {"fwd": 6, "bwd": 14, "train": 20, "decode": 2, "ep_fwd": 10, "ep_bwd": 19}
 
 
 def measured_peaks():
@@ -83,6 +101,7 @@ class ClockSampler:
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+        return self
 
     def stop(self):
         if self.proc is None:
@@ -112,29 +131,59 @@ class ClockSampler:
         return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
 
 
-def make_workload(name, weights_on=None):
+def make_workload(name, weights_on=None, token_seed=None, weights=None):
+    """Inputs of a workload.  `token_seed` redraws the routing and the activations (not the
+    weights) from another seed: the ranks of a weak-scaled run own different tokens.  `weights`
+    (the four weight tensors of an earlier workload of the same shape) skips drawing them again;
+    routing and activations are what `make_inputs` draws first from the same seed."""
     import torch
     from yamoe_b200 import workloads
     w = WORKLOADS[name]
     dtype = torch.float32 if w.get("fp32") else torch.bfloat16
-    if name == "readme_fp32_t512":
+    if weights is not None:
+        gen = torch.Generator().manual_seed(42)
+        idx, dense = workloads.make_routing(w["T"], w["E"], w["K"], gen)
+        inp = dict(hidden_states=torch.randn(w["T"], w["H"], generator=gen).to(dtype), router_indices=idx,
+                   routing_weights=dense.to(dtype))
+        inp.update(zip(KEYS[3:], weights))
+    elif name == "readme_fp32_t512":
         inp = workloads.make_readme_inputs(batch=2)
     else:
         big = w["E"] * w["H"] * w["H"] * 3 > 2 ** 31          # 120B-shaped: draw the weights on the device
         inp = workloads.make_inputs(w["T"], w["H"], w["E"], w["K"], seed=42, dtype=dtype,
                                     skew=w.get("skew", False), with_grad=(w["mode"] in ("bwd", "train")),
                                     weights_on=weights_on if big else None)
+        if token_seed is not None:
+            gen = torch.Generator().manual_seed(token_seed)
+            idx, dense = workloads.make_routing(w["T"], w["E"], w["K"], gen)
+            inp["router_indices"], inp["routing_weights"] = idx, dense.to(dtype)
+            inp["hidden_states"] = torch.randn(w["T"], w["H"], generator=gen).to(dtype)
     return w, inp, dtype
 
 
-def cpu_reference_time(w, inp, dtype, limit_s=20.0, threads=None):
-    """Times the CPU port of the reference forward (sparse per-expert loop) in the workload's
-    dtype.  Returns (tokens_per_s, cores, sample description)."""
-    import torch
+# ---- CPU side: the reference's own PyTorch implementation when a copy travelled with the tree ------
+def cpu_impl():
+    """(kind, forward_fn, backward_fn).  `oracle/_ref/reference.py` is the reference project's
+    own file (placed there by oracle/make_ref.py where the reference tree is present); otherwise the
+    CPU restatement in oracle/experts_oracle.py is timed."""
     from oracle import experts_oracle as orc
+    path = os.path.join(ROOT, "oracle", "_ref", "reference.py")
+    if os.path.exists(path):
+        try:
+            return "reference", orc.reference_forward_from(path), orc.experts_backward_oracle
+        except Exception:      # unusable copy: time the restatement
+            pass
+    return "port", orc.experts_forward_oracle, orc.experts_backward_oracle
+
+
+def cpu_reference_time(w, inp, dtype, limit_s=20.0, threads=None):
+    """Times the CPU forward (sparse per-expert loop) in the workload's dtype.
+    Returns (tokens_per_s, cores, sample description, kind)."""
+    import torch
     if threads:
         torch.set_num_threads(threads)
     cores = torch.get_num_threads()
+    kind, fwd, bwd = cpu_impl()
     T, E, K = w["T"], w["E"], w["K"]
     args = [inp[k] for k in KEYS]
     cap = 256 if w.get("fp32") else T
@@ -143,15 +192,16 @@ def cpu_reference_time(w, inp, dtype, limit_s=20.0, threads=None):
         t0 = time.perf_counter()
         with torch.no_grad():
             if w["mode"] in ("bwd", "train"):
-                orc.experts_backward_oracle(inp["grad_out"], *args, cap, E, K, compute_dtype=dtype)
+                bwd(inp["grad_out"], *args, cap, E, K, compute_dtype=dtype)
             if w["mode"] in ("fwd", "train"):
-                orc.experts_forward_oracle(*args, cap, E, K, compute_dtype=dtype)
+                fwd(*args, cap, E, K, compute_dtype=dtype)
         return time.perf_counter() - t0
 
     first = run()                               # warm-up, also sizes the sample
     reps = max(1, min(3, int(limit_s / max(first, 1e-3)) - 1))
     best = min([run() for _ in range(reps)] + ([first] if reps == 1 and first > limit_s / 2 else []))
-    return T / best, cores, f"full workload ({T} tokens), best of {reps} after 1 warm-up, {dtype}, {cores} threads"
+    return (T / best, cores,
+            f"full workload ({T} tokens), best of {reps} after 1 warm-up, {dtype}, {cores} threads", kind)
 
 
 def run_reference(args):
@@ -164,15 +214,15 @@ def run_reference(args):
     torch.set_num_threads(os.cpu_count() or 1)
     T = w["T"]
     args_list = [inp[k] for k in KEYS]
-    from oracle import experts_oracle as orc
+    kind, fwd, bwd = cpu_impl()
     cap = 256 if w.get("fp32") else T
 
     def step():
         with torch.no_grad():
             if w["mode"] in ("bwd", "train"):
-                orc.experts_backward_oracle(inp["grad_out"], *args_list, cap, w["E"], w["K"], compute_dtype=dtype)
+                bwd(inp["grad_out"], *args_list, cap, w["E"], w["K"], compute_dtype=dtype)
             if w["mode"] in ("fwd", "train"):
-                orc.experts_forward_oracle(*args_list, cap, w["E"], w["K"], compute_dtype=dtype)
+                fwd(*args_list, cap, w["E"], w["K"], compute_dtype=dtype)
 
     steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
     for _ in range(warm):
@@ -183,6 +233,8 @@ def run_reference(args):
     dt = (time.perf_counter() - t0) / steps
     cores = torch.get_num_threads()
     val = T / dt
+    what = ("the reference's own reference.py (GptOssExperts, sparse branch)" if kind == "reference"
+            else "CPU port of the reference's PyTorch experts (sparse branch)")
     line = {
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
@@ -190,9 +242,8 @@ def run_reference(args):
         "data": "synthetic (seeded, shapes of the reference's own benchmarks)",
         "config": {"workload": args.workload, "tokens": T, "hidden": w["H"], "experts": w["E"], "top_k": w["K"],
                    "pass": w["mode"]},
-        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": f"full workload ({T} tokens) per step, {steps} steps, CPU port of the "
-                                   f"reference's PyTorch experts (sparse branch), {cores} threads"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": kind,
+                         "sample": f"full workload ({T} tokens) per step, {steps} steps, {what}, {cores} threads"},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -250,104 +301,175 @@ def copy_bandwidth(torch, nbytes=64 << 20):
     return out
 
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-    import yamoe_b200
-    from yamoe_b200 import _lib
+class Env:
+    """Process-wide facts of a run."""
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device; yamoe_b200 has no CPU fallback")
-    torch.cuda.set_device(local_rank)
-    host_place = place_near_gpu(local_rank)
-    allowed_cpus = host_place.pop("_allowed")
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
-    w, inp, dtype = make_workload(args.workload, weights_on="cuda")
-    T, H, E, K = w["T"], w["H"], w["E"], w["K"]
-    cap = 256 if w.get("fp32") else T
-    dev = [inp[k].cuda() for k in KEYS]
-    decode = T * K <= 256
-    distinct = int(torch.unique(inp["router_indices"]).numel())
-    weight_bytes = float(sum(dev[i].numel() * dev[i].element_size() for i in (3, 4, 5, 6)))
-    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda") if decode else None
-    flush_read = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda") if decode else None
-    grad_out = inp["grad_out"].cuda() if w["mode"] in ("bwd", "train") else None
-    if w["mode"] == "train":
-        for i in (0, 2, 3, 4, 5, 6):
-            dev[i].requires_grad_(True)
-    L = _lib.lib()
-    use_ep = bool(w.get("ep")) and world > 1
-    if use_ep:
-        from yamoe_b200 import ep
-        T_total = T
-        lo, hi = rank * (T // world), (rank + 1) * (T // world)
-        local_w = ep.shard_expert_weights(*dev[3:], rank, world)
-        inp = {k: (v[lo:hi] if k in KEYS[:3] + ["grad_out"] else v) for k, v in inp.items()}
-        if grad_out is not None:
-            grad_out = grad_out[lo:hi].contiguous()
-        dev = [dev[i][lo:hi].contiguous() for i in range(3)] + list(local_w)
-        torch.cuda.empty_cache()
-        T = hi - lo
-        ep_stats = {}
-        peer_ctx = None
-        if args.ep_mode in ("peer", "peer-fused") and w["mode"] in ("fwd", "bwd"):
-            peer_ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=T_total, max_tokens_local=T, dtype=dtype,
-                                             fused_return=(args.ep_mode == "peer-fused"),
-                                             backward=(w["mode"] == "bwd"))
+    def sync_all(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
 
-    def step():
-        if use_ep and w["mode"] == "bwd":
-            if peer_ctx is not None:
-                return peer_ctx.backward(grad_out, *dev, cap)
-            return ep.ep_experts_backward(grad_out, *dev, cap, E, K)
-        if use_ep and peer_ctx is not None:
-            return peer_ctx.forward(*dev, cap)
-        if use_ep:
-            return ep.ep_experts(*dev, cap, E, K, stats=ep_stats)
-        if w["mode"] == "bwd":
-            return yamoe_b200.experts_backward(grad_out, *dev, cap, E, K)
+    def max_over_ranks(self, x: float) -> float:
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.item()
+
+
+class Case:
+    """One workload set up on this rank: device tensors and the function that runs one step."""
+
+    def __init__(self, env: Env, name: str, ep_mode: str = "peer", weak: bool = False, weights=None):
+        import yamoe_b200
+        torch = env.torch
+        self.env, self.name, self.ep_mode, self.weak = env, name, ep_mode, weak
+        world, rank = env.world, env.rank
+        self.use_ep = world > 1 and (weak or bool(WORKLOADS[name].get("ep")))
+        w, inp, dtype = make_workload(name, weights_on="cuda", weights=weights,
+                                      token_seed=(42 + 1000 * rank) if (weak and rank > 0) else None)
+        self.w, self.dtype = w, dtype
+        T, H, E, K = w["T"], w["H"], w["E"], w["K"]
+        self.H, self.E, self.K, self.mode = H, E, K, w["mode"]
+        self.cap = 256 if w.get("fp32") else (T * world if weak else T)
+        self.decode = T * K <= 256
+        self.distinct = int(torch.unique(inp["router_indices"]).numel())
+        dev = [inp[k].cuda() for k in KEYS]
+        self.weight_bytes = float(sum(dev[i].numel() * dev[i].element_size() for i in (3, 4, 5, 6)))
+        self.grad_out = inp["grad_out"].cuda() if w["mode"] in ("bwd", "train") else None
+        self.peer_ctx, self.ep_stats, self.ep_check = None, {}, None
+        if self.use_ep:
+            from yamoe_b200 import ep
+            self.ep = ep
+            if weak:
+                T_total, lo, hi = T * world, 0, T
+            else:
+                T_total, lo, hi = T, rank * (T // world), (rank + 1) * (T // world)
+            local_w = ep.shard_expert_weights(*dev[3:], rank, world)
+            inp = {k: (v[lo:hi] if k in KEYS[:3] + ["grad_out"] else v) for k, v in inp.items()}
+            if self.grad_out is not None:
+                self.grad_out = self.grad_out[lo:hi].contiguous()
+            tok = [dev[i][lo:hi].contiguous() for i in range(3)]
+            if ep_mode == "peer" and w["mode"] in ("fwd", "bwd"):
+                self.peer_ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=T_total, max_tokens_local=hi - lo,
+                                                      dtype=dtype, backward=(w["mode"] == "bwd"))
+            if weak:
+                self.ep_check = self._check_against_single_gpu(tok, dev[3:], local_w)
+            dev = tok + list(local_w)
+            torch.cuda.empty_cache()
+            T = hi - lo
+        self.inp, self.dev, self.T = inp, dev, T
         if w["mode"] == "train":
             for i in (0, 2, 3, 4, 5, 6):
-                dev[i].grad = None
-            out = yamoe_b200.experts_autograd(*dev, cap, E, K, True, save_activations=bool(w.get("saved")))
-            out.backward(grad_out)
-            return dev[0].grad
-        return yamoe_b200.experts(*dev, cap, E, K)
+                dev[i].requires_grad_(True)
+        self.yamoe = yamoe_b200
 
-    def sync_all():
+    def _check_against_single_gpu(self, tok, full_w, local_w):
+        """Expert-parallel output of this rank's tokens against the single-GPU op run on the same
+        tokens with all experts; worst rank wins.  bf16 rule of the parity tests."""
+        torch, env = self.env.torch, self.env
+        import yamoe_b200
+        got = self._ep_forward(tok, local_w).float()
+        ref = yamoe_b200.experts(*tok, *full_w, self.cap, self.E, self.K).float()
         torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+        status = self.peer_ctx.status() if self.peer_ctx is not None else 0
+        diff = (got - ref).abs()
+        rel_l2 = float(diff.norm() / ref.norm().clamp_min(1e-30))
+        ratio = float((diff / (2e-2 * ref.abs() + 2e-2 * ref.abs().max())).max())
+        rel_l2, ratio, status = env.max_over_ranks(rel_l2), env.max_over_ranks(ratio), int(env.max_over_ranks(status))
+        return {"rel_l2": rel_l2, "max_ratio": ratio, "device_status": status,
+                "ok": bool(rel_l2 <= 1e-2 and ratio <= 1.0 and status == 0),
+                "rule": "|ep - single| <= 2e-2*|single| + 2e-2*max|single| and rel-L2 <= 1e-2, max over ranks; "
+                        "single = yamoe_b200.experts on this rank's tokens with all experts resident"}
 
-    for _ in range(args.warmup):
-        step()
-    sync_all()
+    def _ep_forward(self, tok, local_w):
+        if self.peer_ctx is not None:
+            return self.peer_ctx.forward(*tok, *local_w, self.cap)
+        return self.ep.ep_experts(*tok, *local_w, self.cap, self.E, self.K, stats=self.ep_stats)
 
-    # ---- device-resident timing, with the gate_up GEMM bracketed by its own events ------------
-    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    def run(self, tok=None, grad=None):
+        """One step on device-resident inputs (`tok` replaces the three per-token tensors)."""
+        dev, cap, E, K, w = self.dev, self.cap, self.E, self.K, self.w
+        a = list(tok) if tok is not None else dev[:3]
+        g = grad if grad is not None else self.grad_out
+        if self.use_ep and w["mode"] == "bwd":
+            if self.peer_ctx is not None:
+                return self.peer_ctx.backward(g, *a, *dev[3:], cap)[0]
+            return self.ep.ep_experts_backward(g, *a, *dev[3:], cap, E, K)[0]
+        if self.use_ep:
+            return self._ep_forward(a, dev[3:])
+        if w["mode"] == "bwd":
+            return self.yamoe.experts_backward(g, *a, *dev[3:], cap, E, K)[0]
+        if w["mode"] == "train":
+            if tok is None:
+                for i in (0, 2, 3, 4, 5, 6):
+                    dev[i].grad = None
+                out = self.yamoe.experts_autograd(*dev, cap, E, K, True, save_activations=bool(w.get("saved")))
+                out.backward(g)
+                return dev[0].grad
+            x = a[0].detach().requires_grad_(True)
+            out = self.yamoe.experts_autograd(x, a[1], a[2], *dev[3:], cap, E, K, False,
+                                              save_activations=bool(w.get("saved")))
+            out.backward(g)
+            return x.grad
+        return self.yamoe.experts(*a, *dev[3:], cap, E, K)
+
+    def rows_processed(self):
+        """Rows this rank's grouped GEMMs process per step."""
+        if self.use_ep and self.peer_ctx is not None:
+            lay_counts = self.peer_ctx.ctrl.view(-1)[: 2 * self.env.world * self.E].view(2, self.env.world, self.E)
+            per = self.E // self.env.world
+            epoch = int(self.peer_ctx.state[0])
+            return int(lay_counts[epoch & 1, :, self.env.rank * per:(self.env.rank + 1) * per].sum().item())
+        if self.use_ep:
+            return int(self.ep_stats.get("rows_received", self.T * self.K))
+        return self.T * self.K
+
+    def launches(self):
+        if self.decode:
+            return LAUNCHES["decode"]
+        if self.use_ep and self.peer_ctx is not None:
+            return LAUNCHES["ep_" + self.mode]
+        return LAUNCHES[self.mode]
+
+
+def time_resident(case: Case, steps: int, warmup: int, sample_clocks: bool = True):
+    """Device-resident timing of `steps` steps: ms per step (max over ranks), the gate_up GEMM's
+    device time inside every step (forward workloads), clock samples taken meanwhile."""
+    from yamoe_b200 import _lib
+    env, torch = case.env, case.env.torch
+    L = _lib.lib()
+    for _ in range(warmup):
+        case.run()
+    env.sync_all()
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     for a, b in pairs:
         a.record(); b.record()           # forces creation of the underlying cudaEvent_t
     torch.cuda.synchronize()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler = ClockSampler(env.local_rank).start() if sample_clocks else None
     t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    if decode:
+    env.sync_all()
+    eager_us = None
+    if case.decode:
         # Touched weights (0.2 - 5.8 GB) are comparable to the 126 MB L2 at T=1: flush it between
         # steps and time every step by itself.  A call is ~50 us of GPU work but more than that of
         # Python dispatch, so the whole-call time is taken from a CUDA-graph replay of the same call
         # (the op issues only kernel launches); the gate_up kernel time comes from a second,
-        # ungraphed pass with the stage events.
+        # ungraphed pass with the stage events, which also gives the eager (ungraphed) call time.
+        flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+        flush_read = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            graph_out = step()
-        sync_all()
+            case.run()
+        env.sync_all()
         step_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in pairs]
         for s0, s1 in step_ev:
             flush_buf.fill_(1)             # 256 MB written: evicts the workload from the 126 MB L2 ...
@@ -356,42 +478,53 @@ def run_ours(args):
             s0.record()
             graph.replay()
             s1.record()
-        sync_all()
+        env.sync_all()
         ms_total = sum(s0.elapsed_time(s1) for s0, s1 in step_ev)
+        eager = []
         for a, b in pairs:
             flush_buf.fill_(1)
             flush_read.sum()
+            torch.cuda.synchronize()
             L.yamoe_b200_set_stage_events(a.cuda_event, b.cuda_event, 1)
-            step()
-        sync_all()
+            t0 = time.perf_counter()
+            case.run()
+            torch.cuda.synchronize()
+            eager.append((time.perf_counter() - t0) * 1e6)
+        eager_us = statistics.median(eager)
+        env.sync_all()
+        del flush_buf, flush_read
     else:
         t_start.record()
         for a, b in pairs:
             L.yamoe_b200_set_stage_events(a.cuda_event, b.cuda_event, 1)
-            step()
+            case.run()
         t_stop.record()
-        sync_all()
+        env.sync_all()
         ms_total = t_start.elapsed_time(t_stop)
     L.yamoe_b200_set_stage_events(None, None, 0)
-    gemm_ms = [a.elapsed_time(b) for a, b in pairs] if w["mode"] == "fwd" else []
-    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = t.item() / args.steps
-    value = world * T / (ms_step * 1e-3)
+    clocks = sampler.stop() if sampler is not None else None
+    gemm_ms = [a.elapsed_time(b) for a, b in pairs] if case.mode == "fwd" else []
+    ms_step = env.max_over_ranks(ms_total) / steps
+    status = case.peer_ctx.status() if case.peer_ctx is not None else 0
+    return dict(ms_step=ms_step, gemm_ms=gemm_ms, clocks=clocks, eager_us=eager_us, device_status=status)
 
-    # ---- end to end: host inputs in, host result out, every step -------------------------------
-    host_in = [inp[k].pin_memory() for k in KEYS[:3]]
+
+def time_e2e(case: Case, steps: int, warmup: int, eager: bool):
+    """End to end: host inputs in, host result out, every step.  Returns (tokens/s over all ranks,
+    h2d bytes, d2h bytes, description of the pipeline)."""
+    env, torch = case.env, case.env.torch
+    w, T, H, dtype = case.w, case.T, case.H, case.dtype
+    host_in = [case.inp[k].pin_memory() for k in KEYS[:3]]
     host_out = torch.empty(T, H, dtype=dtype).pin_memory()
-    host_go = inp["grad_out"].pin_memory() if w["mode"] in ("bwd", "train") else None
+    host_go = case.inp["grad_out"].pin_memory() if w["mode"] in ("bwd", "train") else None
     h2d = sum(x.numel() * x.element_size() for x in host_in) + (host_go.numel() * host_go.element_size() if host_go is not None else 0)
     d2h = host_out.numel() * host_out.element_size()
 
     # Three streams pipeline consecutive steps: while step i computes, step i+1's inputs come in and
     # step i-1's result goes out (PCIe is full duplex).  Every step still copies its own inputs from
     # pinned host memory and its own result back; expert-parallel steps stay on one stream because
-    # their collectives must be issued in the same order on every rank.
-    pipelined = not use_ep
+    # all calls of a rank share its peer-writable buffers.
+    pipelined = not case.use_ep
     cur = torch.cuda.current_stream()
     s_in, s_out = (torch.cuda.Stream(), torch.cuda.Stream()) if pipelined else (cur, cur)
     host_outs = [host_out, torch.empty_like(host_out).pin_memory()]
@@ -401,24 +534,6 @@ def run_ours(args):
     keep = [None, None]
     dev_in = [[torch.empty_like(x, device="cuda") for x in host_in] for _ in range(2)]
     dev_go = [torch.empty_like(host_go, device="cuda") if host_go is not None else None for _ in range(2)]
-
-    def run_op(a, g):
-        if w["mode"] == "train":
-            x = a[0].detach().requires_grad_(True)
-            out = yamoe_b200.experts_autograd(x, a[1], a[2], *dev[3:], cap, E, K, False,
-                                              save_activations=bool(w.get("saved")))
-            out.backward(g)
-            return x.grad
-        if w["mode"] == "bwd":
-            if use_ep:
-                outs = (peer_ctx.backward(g, *a, *dev[3:], cap) if peer_ctx is not None
-                        else ep.ep_experts_backward(g, *a, *dev[3:], cap, E, K))
-            else:
-                outs = yamoe_b200.experts_backward(g, *a, *dev[3:], cap, E, K)
-            return outs[0]
-        if use_ep:
-            return peer_ctx.forward(*a, *dev[3:], cap) if peer_ctx is not None else ep.ep_experts(*a, *dev[3:], cap, E, K)
-        return yamoe_b200.experts(*a, *dev[3:], cap, E, K)
 
     def e2e_step(i):
         b = i % 2
@@ -431,7 +546,7 @@ def run_ours(args):
                 g.copy_(host_go, non_blocking=True)
             in_ready[b].record(s_in)
         cur.wait_event(in_ready[b])
-        out = run_op(a, g)
+        out = case.run(a, g)
         comp_done[b].record(cur)
         with torch.cuda.stream(s_out):
             s_out.wait_event(comp_done[b])
@@ -446,7 +561,7 @@ def run_ours(args):
     # cannot fall behind the GPU.  Three graphs with their own buffers take turns on three streams,
     # so consecutive steps overlap as in the eager pipeline.  Anything else keeps the eager pipeline.
     graphs = None
-    if pipelined and w["mode"] == "fwd" and not args.eager_e2e:
+    if pipelined and w["mode"] == "fwd" and not eager:
         try:
             graphs = []
             g_streams = [s_in, s_out, torch.cuda.Stream()]
@@ -457,7 +572,7 @@ def run_ours(args):
                 with torch.cuda.graph(gph):
                     for d_, h_ in zip(g_in[b], host_in):
                         d_.copy_(h_, non_blocking=True)
-                    g_out[b].copy_(run_op(g_in[b], None), non_blocking=True)
+                    g_out[b].copy_(case.run(g_in[b], None), non_blocking=True)
                 graphs.append(gph)
         except Exception as exc:           # capture not possible here: time the eager pipeline
             sys.stderr.write(f"bench.py: CUDA-graph capture of the end-to-end step failed ({exc!r}); eager pipeline\n")
@@ -469,95 +584,197 @@ def run_ours(args):
             graphs[i % 3].replay()
 
     step_fn = graph_step if graphs is not None else e2e_step
-    for i in range(min(args.warmup, 3) if graphs is None else 6):
+    for i in range(min(warmup, 3) if graphs is None else 6):
         step_fn(i)
-    sync_all()
+    env.sync_all()
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
     s_in.wait_event(e_start)
     s_out.wait_event(e_start)
     if graphs is not None:
         g_streams[2].wait_event(e_start)
-    for i in range(args.steps):
+    for i in range(steps):
         step_fn(i)
     cur.wait_stream(s_in)
     cur.wait_stream(s_out)
     if graphs is not None:
         cur.wait_stream(g_streams[2])
     e_stop.record()
-    sync_all()
-    clocks = sampler.stop()
-    te = torch.tensor([e_start.elapsed_time(e_stop)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_value = world * T / (te.item() / args.steps * 1e-3)
+    env.sync_all()
+    ms = env.max_over_ranks(e_start.elapsed_time(e_stop))
+    value = env.world * T / (ms / steps * 1e-3)
+    how = ("every step is one CUDA-graph replay of (host->device copies, op, device->host copy); "
+           "three such graphs take turns on three streams, so consecutive steps overlap"
+           if graphs is not None else
+           "host->device copy, op and device->host copy of consecutive steps overlap on three streams"
+           if pipelined else "one stream, copies and op in sequence")
+    return value, h2d, d2h, how
 
+
+def roofline_of(case: Case, res, peaks, rows):
+    """`roofline` object of the JSON line for the dominant kernel of a forward workload."""
+    torch = case.env.torch
+    gemm_ms, H = res["gemm_ms"], case.H
+    if not gemm_ms:
+        return None
+    mean_ms = sum(gemm_ms) / len(gemm_ms)
+    if case.decode:
+        kbytes = case.distinct * (H * 2 * H * 2 + 2 * H * 2)          # gate_up weights + bias of the touched experts
+        achieved = kbytes / (mean_ms * 1e-3) / 1e9
+        return {"bound": "hbm", "kernel": "gemv_kernel<gate_up + bias + clamped SwiGLU>",
+                "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel_ms": mean_ms,
+                "peak_source": peaks["source"] + " (copy bandwidth)",
+                "frac_of_nominal_8000": achieved / 8000.0, "distinct_experts": case.distinct,
+                "whole_op_gbs": case.distinct * 49783680 / (res["ms_step"] * 1e-3) / 1e9}
+    if case.dtype == torch.float32:
+        # fp32 runs on the CUDA cores (FFMA): no measured peak exists for that pipe, so the
+        # fraction is against the nominal 148 SMs x 128 FMA x 2 x 1.965 GHz
+        achieved = 4.0 * rows * H * H / (mean_ms * 1e-3) / 1e12
+        ffma_peak = 148 * 128 * 2 * 1.965e9 / 1e12
+        return {"bound": "tensor", "kernel": "simt_gemm_kernel<gate_up + bias + clamped SwiGLU> (fp32 FFMA)",
+                "achieved": achieved, "peak": ffma_peak, "unit": "TFLOP/s", "frac": achieved / ffma_peak,
+                "traffic": None, "kernel_ms": mean_ms,
+                "peak_source": "nominal fp32 FFMA rate (CUDA cores; the tensor pipe is not used in fp32)"}
+    achieved = 4.0 * rows * H * H / (mean_ms * 1e-3) / 1e12
+    tile_n = int(os.environ.get("YAMOE_B200_BN", "256") or 256)
+    traffic, source = TRAFFIC.get((case.name, tile_n), (None, None)) if not case.use_ep else (None, None)
+    return {"bound": "tensor", "kernel": "umma_gemm_kernel<gate_up + bias + clamped SwiGLU>",
+            "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": achieved / peaks["bf16_tflops"], "traffic": traffic, "traffic_source": source,
+            "kernel_ms": mean_ms, "peak_source": peaks["source"] + " (burst bf16 matmul)",
+            "frac_of_nominal_2250": achieved / 2250.0, "rows": rows}
+
+
+def extras_single_gpu(env: Env, peaks):
+    """Decode (T = 1, 4, 16, 64) and backward (T = 8192) under the same clock, one GPU."""
+    out = {"decode": [], "bwd": None}
+    weights = None
+    for T in (1, 4, 16, 64):
+        case = Case(env, f"gptoss120b_decode_t{T}", weights=weights)
+        weights = case.dev[3:]               # 12.7 GB of expert weights: drawn once
+        res = time_resident(case, 40, 5)
+        roof = roofline_of(case, res, peaks, case.T * case.K)
+        out["decode"].append({"T": T, "us": res["ms_step"] * 1e3, "distinct_experts": case.distinct,
+                              "whole_op_gbs": roof["whole_op_gbs"],
+                              "frac_of_measured_hbm": roof["whole_op_gbs"] / peaks["hbm_gbs"],
+                              "gate_up_frac": roof["frac"], "eager_call_us": res["eager_us"],
+                              "clocks": res["clocks"]})
+        del case
+    del weights
+    env.torch.cuda.empty_cache()
+    case = Case(env, "gptoss20b_bwd_t8192")
+    res = time_resident(case, 10, 3)
+    S = case.T * case.K
+    tf = 16.0 * S * case.H * case.H / (res["ms_step"] * 1e-3) / 1e12
+    out["bwd"] = {"workload": "gptoss20b_bwd_t8192", "ms": res["ms_step"], "tflops": tf,
+                  "frac": tf / peaks["bf16_tflops"], "algorithmic_flops": "16*S*H^2", "clocks": res["clocks"]}
+    del case
+    env.torch.cuda.empty_cache()
+    return out
+
+
+def extras_multi_gpu(env: Env):
+    """Strong-scaling expert-parallel workloads, peer-store and NCCL all-to-all exchange."""
+    out = []
+    for name in ("gptoss20b_fwd_t8192_ep", "gptoss20b_bwd_t8192_ep", "gptoss120b_prefill_t16384"):
+        for mode in ("peer", "nccl"):
+            case = Case(env, name, ep_mode=mode)
+            res = time_resident(case, 10 if case.mode == "bwd" else 20, 3, sample_clocks=False)
+            rows = case.rows_processed()
+            out.append({"workload": name, "ep_mode": mode, "ms_per_step": res["ms_step"],
+                        "tokens_per_s": WORKLOADS[name]["T"] / (res["ms_step"] * 1e-3),
+                        "rank0_row_share": rows / float(WORKLOADS[name]["T"] * case.K),
+                        "device_status": res["device_status"]})
+            del case
+            env.torch.cuda.empty_cache()
+            env.sync_all()
+    return out
+
+
+def run_ours(args):
+    env = Env()
+    torch, dist = env.torch, env.dist
+    world, rank, local_rank = env.world, env.rank, env.local_rank
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; yamoe_b200 has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    host_place = place_near_gpu(local_rank)
+    allowed_cpus = host_place.pop("_allowed")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    weak_ep = world > 1 and args.workload == DEFAULT
+    case = Case(env, args.workload, ep_mode=args.ep_mode, weak=weak_ep)
+    w, T, H, E, K, dtype = case.w, case.T, case.H, case.E, case.K, case.dtype
+    if case.ep_check is not None and not case.ep_check["ok"]:
+        if rank == 0:
+            print(json.dumps({"metric": "moe_layer_tokens_per_s", "value": None, "n_gpus": world,
+                              "ep_check": case.ep_check, "error": "expert-parallel output differs from the single-GPU op"}),
+                  flush=True)
+        dist.destroy_process_group()
+        sys.exit(1)
+
+    res = time_resident(case, args.steps, args.warmup)
+    ms_step = res["ms_step"]
+    value = world * T / (ms_step * 1e-3)
+    rows = case.rows_processed()
+    e2e_value, h2d, d2h, how = time_e2e(case, args.steps, args.warmup, args.eager_e2e)
+
+    line = None
     if rank == 0:
         peaks = measured_peaks()
-        if use_ep and peer_ctx is not None:
-            per = E // world
-            ep_stats["rows_received"] = int(peer_ctx.counts_all[:, rank * per:(rank + 1) * per].sum().item())
-        S = ep_stats.get("rows_received", T * K) if use_ep else T * K      # rows this rank's GEMMs process
+        if case.use_ep:
+            exch = ("dispatch + combine as NVLink peer stores issued by the dispatch kernel and by the down GEMM's "
+                    "epilogue, counts and phase boundaries as flags in symmetric memory, no collective call, no host sync"
+                    if case.peer_ctx is not None else
+                    "NCCL all-to-all dispatch + combine; rank-0 rows sent/received "
+                    f"{case.ep_stats.get('rows_sent')}/{case.ep_stats.get('rows_received')}")
+            par = (f"ep{world} (" + (f"{T} tokens per rank, " if weak_ep else "tokens sharded by rows, ")
+                   + f"experts sharded contiguously {E // world} per rank; {exch})")
+        else:
+            par = f"dp{world} (token shards, replicated experts, no collective)"
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "strong" if use_ep else "weak", "vs_baseline": None,
+            "scaling": "weak" if (weak_ep or not case.use_ep) else "strong", "vs_baseline": None,
             "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
             "data": "synthetic (seeded, shapes of the reference's own benchmarks)",
-            "config": {"workload": args.workload, "tokens": T, "hidden": H, "experts": E, "top_k": K,
-                       "pass": w["mode"], "expert_capacity": cap,
-                       "parallelism": (f"ep{world} (tokens sharded by rows, experts sharded contiguously, "
-                                       + (f"dispatch + combine as NVLink peer stores [{args.ep_mode}], offsets on device, no host sync)"
-                                          if use_ep and peer_ctx is not None else
-                                          "NCCL all-to-all dispatch + combine; rank-0 rows sent/received "
-                                          f"{ep_stats.get('rows_sent')}/{ep_stats.get('rows_received')})")) if use_ep else
-                                      f"dp{world} (token shards, replicated experts, no collective)",
-                       "l2": ("L2 flushed (256 MB write, then 256 MB read to drain the dirty lines) between steps; each step is a CUDA-graph replay of the op call timed by its own events" if decode
-                              else f"expert weights ({weight_bytes / 1e9:.1f} GB) exceed the 126 MB L2; no flush")},
+            "config": {"workload": args.workload, "tokens": T * world if weak_ep else w["T"], "tokens_per_rank": T,
+                       "hidden": H, "experts": E, "top_k": K, "pass": w["mode"], "expert_capacity": case.cap,
+                       "parallelism": par,
+                       "l2": ("L2 flushed (256 MB write, then 256 MB read to drain the dirty lines) between steps; each step is a CUDA-graph replay of the op call timed by its own events" if case.decode
+                              else f"expert weights ({case.weight_bytes / 1e9:.1f} GB) exceed the 126 MB L2; no flush")},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "pipeline": ("every step is one CUDA-graph replay of (host->device copies, op, device->host copy); "
-                                 "three such graphs take turns on three streams, so consecutive steps overlap"
-                                 if graphs is not None else
-                                 "host->device copy, op and device->host copy of consecutive steps overlap on three streams"
-                                 if pipelined else "one stream, copies and op in sequence"),
-                    "host": dict(host_place, **copy_bandwidth(torch))},
-            "gpu_launches": args.steps * (2 if decode else {"fwd": 6, "bwd": 14, "train": 20}[w["mode"]]),
-            "clocks": clocks,
-            "achieved_tflops_whole_op": {"fwd": 6, "bwd": 16, "train": 22}[w["mode"]] * S * H * H / (ms_step * 1e-3) / 1e12,
+                    "pipeline": how, "host": dict(host_place, **copy_bandwidth(torch))},
+            "gpu_launches": args.steps * case.launches(),
+            "clocks": res["clocks"],
+            "achieved_tflops_whole_op": {"fwd": 6, "bwd": 16, "train": 22}[w["mode"]] * rows * H * H / (ms_step * 1e-3) / 1e12,
+            "device_status": res["device_status"],
         }
-        if gemm_ms and decode:
-            mean_ms = sum(gemm_ms) / len(gemm_ms)
-            kbytes = distinct * (H * 2 * H * 2 + 2 * H * 2)          # gate_up weights + bias of the touched experts
-            achieved = kbytes / (mean_ms * 1e-3) / 1e9
-            line["roofline"] = {"bound": "hbm", "kernel": "gemv_kernel<gate_up + bias + clamped SwiGLU>",
-                                "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel_ms": mean_ms,
-                                "peak_source": peaks["source"] + " (copy bandwidth)",
-                                "frac_of_nominal_8000": achieved / 8000.0, "distinct_experts": distinct,
-                                "whole_op_gbs": distinct * 49783680 / (ms_step * 1e-3) / 1e9}
-        elif gemm_ms and dtype == torch.float32:
-            # fp32 runs on the CUDA cores (FFMA): no measured peak exists for that pipe, so the
-            # fraction is against the nominal 148 SMs x 128 FMA x 2 x 1.965 GHz
-            mean_ms = sum(gemm_ms) / len(gemm_ms)
-            achieved = 4.0 * S * H * H / (mean_ms * 1e-3) / 1e12
-            ffma_peak = 148 * 128 * 2 * 1.965e9 / 1e12
-            line["roofline"] = {"bound": "tensor", "kernel": "simt_gemm_kernel<gate_up + bias + clamped SwiGLU> (fp32 FFMA)",
-                                "achieved": achieved, "peak": ffma_peak, "unit": "TFLOP/s", "frac": achieved / ffma_peak,
-                                "traffic": None, "kernel_ms": mean_ms,
-                                "peak_source": "nominal fp32 FFMA rate (CUDA cores; the tensor pipe is not used in fp32)"}
-        elif gemm_ms:
-            mean_ms = sum(gemm_ms) / len(gemm_ms)
-            achieved = 4.0 * S * H * H / (mean_ms * 1e-3) / 1e12
-            line["roofline"] = {"bound": "tensor", "kernel": "umma_gemm_kernel<gate_up + bias + clamped SwiGLU>",
-                                "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                                "frac": achieved / peaks["bf16_tflops"],
-                                "traffic": args.traffic if args.workload == "gptoss20b_fwd_t4096" else None,
-                                "kernel_ms": mean_ms, "peak_source": peaks["source"] + " (burst bf16 matmul)",
-                                "frac_of_nominal_2250": achieved / 2250.0}
-        if world == 1 and not args.no_cpu_baseline:
+        if case.ep_check is not None:
+            line["ep_check"] = case.ep_check
+        roof = roofline_of(case, res, peaks, rows)
+        if roof is not None:
+            line["roofline"] = roof
+        if case.decode:
+            line["eager_call_us"] = res["eager_us"]
+    cpu_inp = {k: t.cpu() for k, t in case.inp.items()} if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
+    del case
+    torch.cuda.empty_cache()
+
+    if not args.no_extras and args.workload == DEFAULT:
+        try:
+            extra = extras_single_gpu(env, measured_peaks()) if world == 1 else extras_multi_gpu(env)
+        except Exception as exc:       # the headline numbers stand; say what went wrong
+            extra = {"error": repr(exc)}
+        if line is not None:
+            line["extra"] = extra
+    if line is not None:
+        if cpu_inp is not None:
             os.sched_setaffinity(0, allowed_cpus)      # the CPU baseline may use every core again
-            v, cores, sample = cpu_reference_time(w, {k: t.cpu() for k, t in inp.items()}, dtype)
-            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+            v, cores, sample, kind = cpu_reference_time(w, cpu_inp, dtype)
+            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -569,14 +786,14 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gptoss20b_fwd_t4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the `extra` measurements that follow the default workload")
     ap.add_argument("--eager-e2e", action="store_true",
                     help="time the end-to-end leg with eager calls on three streams instead of CUDA-graph replays")
-    ap.add_argument("--ep-mode", default="peer", choices=["peer", "peer-fused", "nccl"],
+    ap.add_argument("--ep-mode", default="peer", choices=["peer", "nccl"],
                     help="exchange used by the expert-parallel workloads on N > 1 GPUs")
-    ap.add_argument("--traffic", type=float, default=1.268e9,
-                    help="DRAM bytes per launch of the dominant kernel from an ncu capture (see profiles/)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

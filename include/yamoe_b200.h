@@ -68,7 +68,8 @@ int yamoe_b200_set_stage_events(void *start_event, void *stop_event, int stage);
  *   sorted_indices  int32 [T*K]  out   flat position p of each sorted entry (ties: ascending p)
  *   bins            int32 [E+1]  out   bins[e] = number of assignments with id <= e; bins[E] = 0
  *   counts          int32 [E]    out   per-expert histogram (may be NULL)
- * Bit-exact and deterministic.  Ids outside [0,E) are dropped from all outputs.
+ * Bit-exact and deterministic.  Ids outside [0,E) are dropped from all outputs: the kept entries
+ * come first and the remaining entries of sorted_values / sorted_indices read -1.
  * ------------------------------------------------------------------------------------------- */
 size_t yamoe_b200_route_workspace_bytes(int64_t T, int E, int K);
 int yamoe_b200_route(const int64_t *router_indices, int32_t *sorted_values, int32_t *sorted_indices,
@@ -171,12 +172,14 @@ int yamoe_b200_batch_mm(const void *x, const void *weights, void *out, int E, in
  *   permute_rows   dst[j,:] = src[sorted_indices[j] / K, :]          rows in expert-sorted order
  *   combine_rows   out[t,:] = sum_k w[t,k] * rows[pos(t*K+k), :]      pos = inverse of sorted_indices
  * `sorted_indices` is the output of yamoe_b200_route (n_sorted entries; assignments missing from
- * it contribute nothing).  combine_rows needs a workspace of T*K*4 bytes and accumulates in fp32
+ * it contribute nothing; entries that are negative or not below n_src*K -- the -1 tail that route
+ * leaves for dropped ids -- give a zero row in permute_rows and are skipped by combine_rows).
+ * `src` has n_src rows.  combine_rows needs a workspace of T*K*4 bytes and accumulates in fp32
  * in slot order, so it is deterministic.  The weights come from routing_weights[t, expert] when
  * routing_cols == E and from routing_weights[t, k] when routing_cols == K, as in the forward op.
  * ------------------------------------------------------------------------------------------- */
-int yamoe_b200_permute_rows(const void *src, const int32_t *sorted_indices, void *dst, int64_t S, int H, int K,
-                            int dtype, void *stream);
+int yamoe_b200_permute_rows(const void *src, int64_t n_src, const int32_t *sorted_indices, void *dst, int64_t S,
+                            int H, int K, int dtype, void *stream);
 int yamoe_b200_combine_rows(const void *rows, const int32_t *sorted_indices, int64_t n_sorted,
                             const int64_t *router_indices, const void *routing_weights, int routing_cols,
                             void *out, int64_t T, int H, int E, int K, int dtype, void *workspace,
@@ -247,6 +250,64 @@ int yamoe_b200_ep_local_backward(const void *recv_x, const void *recv_g, const f
                                  void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Expert parallelism as ONE call per rank (no counterpart in the reference, which is single-GPU).
+ * The count exchange and the phase boundaries of the peer-store path above are flags in
+ * peer-writable memory instead of host-issued collectives: a call enqueues a fixed chain of
+ * kernels on `stream` and nothing else -- no NCCL call, no host synchronisation, no split sizes.
+ *
+ * Buffers (each allocated by every rank with the same size and made peer-accessible; the
+ * peer_* members are DEVICE arrays of G pointers, index = rank, own buffer included):
+ *   recv_x [max_rows, H] dtype   rows received for this rank's experts (padded expert-sorted layout)
+ *   back   [back_rows, H] dtype  result rows of this rank's own assignments, in its sorted order
+ *   ctrl   yamoe_b200_ep_ctrl_bytes(G, E) bytes, zeroed once before the first call on any rank
+ *   recv_g [max_rows, H] dtype, recv_w [max_rows] fp32, back_w [back_rows] fp32   (backward only)
+ * `state` is 256 bytes of this rank's private device memory, zeroed once; it holds the call
+ * counter (epoch) that the flags carry.  All ranks must make the same sequence of calls.
+ * max_rows must be a multiple of 128 and at least (assignments of all ranks that can land on one
+ * rank) + 128 * E/G; a call whose rows would not fit stores nothing and reports device status 7.
+ *
+ * Every device-side wait (for the counts, for the dispatched rows, for the returned rows) polls
+ * this GPU's own memory and gives up after `wait_ns` nanoseconds (0 = 2 s): the call then leaves
+ * device status 4, 5 or 6 in the workspace header (yamoe_b200_device_status), its outputs are
+ * invalid, and the GPU and all buffers stay usable.
+ * Received receive-buffer padding rows must hold finite values for the backward pass: zero
+ * recv_x and recv_g once before the first call.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t G, rank, E, K, H, dtype;
+  int64_t max_rows;   /* rows of recv_x / recv_g / recv_w */
+  int64_t back_rows;  /* rows of back / back_w; every call needs T*K <= back_rows */
+  void *const *peer_recv_x, *const *peer_recv_g, *const *peer_recv_w;
+  void *const *peer_back, *const *peer_back_w, *const *peer_ctrl;
+  void *recv_x, *recv_g, *recv_w, *back, *back_w, *ctrl; /* this rank's own buffers */
+  void *state;
+  uint64_t wait_ns;
+} yamoe_ep_ctx_t;
+
+size_t yamoe_b200_ep_ctrl_bytes(int G, int E);
+size_t yamoe_b200_ep_call_workspace_bytes(const yamoe_ep_ctx_t *ctx, int64_t T, int backward);
+/* out [T,H] = this rank's token shard through all E experts; arguments as yamoe_b200_experts_forward
+ * with the four weight tensors holding this rank's E/G experts only. */
+int yamoe_b200_ep_forward(const yamoe_ep_ctx_t *ctx, const void *hidden_states, const int64_t *router_indices,
+                          const void *routing_weights, int routing_cols, const void *gate_up_proj,
+                          const void *gate_up_proj_bias, const void *down_proj, const void *down_proj_bias,
+                          void *out, int64_t T, int64_t expert_capacity, void *workspace, size_t workspace_bytes,
+                          void *stream);
+/* Gradients as yamoe_b200_experts_backward (grad_out [T,H]); weight and bias gradients cover this
+ * rank's E/G experts and stay here (experts are not replicated, so nothing is all-reduced). */
+int yamoe_b200_ep_backward(const yamoe_ep_ctx_t *ctx, const void *grad_out, const void *hidden_states,
+                           const int64_t *router_indices, const void *routing_weights, int routing_cols,
+                           const void *gate_up_proj, const void *gate_up_proj_bias, const void *down_proj,
+                           const void *down_proj_bias, void *d_hidden, void *d_routing, void *d_gate_up_proj,
+                           void *d_gate_up_proj_bias, void *d_down_proj, void *d_down_proj_bias, int64_t T,
+                           int64_t expert_capacity, void *workspace, size_t workspace_bytes, void *stream);
+/* Test aid for the give-up path: sets the epoch in `state` to `epoch`, clears `header` (16 int32) and
+ * runs the one-warp wait of the expert-parallel path on `flags[0..G)` with the given limit (0 = 1 ms).
+ * header[4] is 5 afterwards if some flag never reached `epoch`, else 0.  One GPU, no peer involved. */
+int yamoe_b200_ep_wait_probe(const int32_t *flags, int G, int32_t epoch, uint64_t wait_ns, int32_t *state,
+                             int32_t *header, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * The reference's three small sub-operators on its padded [E, C, H] layout.  The expert op of this
  * library never builds that layout; these are for callers of the standalone operators.
  *   binned_gather   replaces gather_cuda        (csrc/gather.cu:68-109, torch-ext/torch_binding.cpp:9-17)
@@ -304,6 +365,12 @@ int yamoe_b200_experts_backward_saved(const void *grad_out, int grad_out_per_slo
  * bounded device-side wait completed, otherwise a code naming the wait that gave up.  Reads
  * 4 bytes from the device with cudaMemcpyAsync on `stream` and synchronises that stream. */
 int yamoe_b200_device_status(const void *workspace, void *stream, int32_t *status_out);
+
+/* Test aid for the give-up path of the grouped GEMM's pipeline waits: clears the 64-byte header at
+ * the start of `workspace` (256-byte aligned, >= 64 bytes) and runs one thread that waits, for at most
+ * `limit_ns` nanoseconds (0 = 1 ms), on a shared-memory barrier nothing arrives at, using the same
+ * bounded wait as the GEMM kernels.  yamoe_b200_device_status on `workspace` then returns 1. */
+int yamoe_b200_mbar_wait_probe(void *workspace, uint64_t limit_ns, void *stream);
 
 #ifdef __cplusplus
 }

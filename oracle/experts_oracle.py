@@ -222,3 +222,35 @@ def check_close(x, ref, rtol, name="", rel_l2=None):
     if rel_l2 is not None:
         assert l2 <= rel_l2, f"{name}: rel-L2 {l2:.3e} > {rel_l2:.1e}"
     return ratio, l2
+
+
+def reference_forward_from(path: str):
+    """Wraps the reference project's own `GptOssExperts` (its reference.py, loaded from `path`) in
+    the signature of `experts_forward_oracle`, running the sparse (training) branch
+    (reference.py:38-59).  The reference has no expert capacity: the wrapper is only valid when the
+    capacity drops nothing, which holds for every benchmark workload."""
+    import importlib.util
+    import types
+    spec = importlib.util.spec_from_file_location("yamoe_reference_py", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    def forward(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias, down_proj,
+                down_proj_bias, expert_capacity, num_experts, top_k, compute_dtype=torch.float32):
+        T, H = hidden_states.shape
+        cfg = types.SimpleNamespace(intermediate_size=H, num_local_experts=num_experts, hidden_size=H)
+        m = mod.GptOssExperts(cfg)
+        for name, t in (("gate_up_proj", gate_up_proj), ("gate_up_proj_bias", gate_up_proj_bias),
+                        ("down_proj", down_proj), ("down_proj_bias", down_proj_bias)):
+            getattr(m, name).data = t.to(compute_dtype)
+        m.train()
+        dense = routing_weights
+        if dense.shape[1] != num_experts:
+            dense = torch.zeros(T, num_experts, dtype=routing_weights.dtype)
+            dense.scatter_(1, router_indices.to(torch.int64), routing_weights)
+        with torch.no_grad():
+            out = m(hidden_states.to(compute_dtype).view(1, T, H), router_indices=router_indices.to(torch.int64),
+                    routing_weights=dense.to(compute_dtype))
+        return out.view(T, H)
+
+    return forward

@@ -97,7 +97,7 @@ def test_permute_and_combine_rows_single_gpu():
         assert half.float().abs().sum() < out.float().abs().sum()
 
 
-def _peer_worker(rank, world, port, q, fused=True):
+def _peer_worker(rank, world, port, q):
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -107,8 +107,7 @@ def _peer_worker(rank, world, port, q, fused=True):
         from yamoe_b200 import ep, workloads
         outs = []
         H, E, K = 256, 16, 4
-        ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=1024, max_tokens_local=512, dtype=torch.bfloat16,
-                                    fused_return=fused)
+        ctx = ep.PeerExpertParallel(H, E, K, max_tokens_total=1024, max_tokens_local=512, dtype=torch.bfloat16)
         # three calls in a row on the same buffers: full capacity, a dropping capacity, fewer tokens
         for T, cap, skew, seed in ((1024, 1024, False, 9), (1024, 100, True, 10), (512, 512, True, 11)):
             inp = workloads.make_inputs(T, H, E, K, seed=seed, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16,
@@ -118,7 +117,24 @@ def _peer_worker(rank, world, port, q, fused=True):
             out = ctx.forward(inp["hidden_states"][lo:hi].cuda(), inp["router_indices"][lo:hi].cuda(),
                               inp["routing_weights"][lo:hi].cuda(), *local_w, cap)
             torch.cuda.synchronize()
+            assert ctx.status() == 0, f"device status {ctx.status()}"
             outs.append(out.float().cpu())
+        # receive buffers too small for a skewed routing: every rank must report the overflow status
+        # (nothing is stored past a buffer), and the same object must serve a fitting call afterwards
+        small = ep.PeerExpertParallel(H, E, K, max_tokens_total=512, max_tokens_local=512, dtype=torch.bfloat16)
+        inp = workloads.make_inputs(1024, H, E, K, seed=10, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16,
+                                    skew=True)
+        lo, hi = rank * 512, (rank + 1) * 512
+        local_w = ep.shard_expert_weights(*[inp[k].cuda() for k in KEYS[3:]], rank, world)
+        small.forward(inp["hidden_states"][lo:hi].cuda(), inp["router_indices"][lo:hi].cuda(),
+                      inp["routing_weights"][lo:hi].cuda(), *local_w, 1024)
+        torch.cuda.synchronize()
+        assert small.status() == 7, f"expected the overflow status, got {small.status()}"
+        out = small.forward(inp["hidden_states"][lo:lo + 128].cuda(), inp["router_indices"][lo:lo + 128].cuda(),
+                            inp["routing_weights"][lo:lo + 128].cuda(), *local_w, 1024)
+        torch.cuda.synchronize()
+        assert small.status() == 0, f"device status {small.status()} after a fitting call"
+        outs.append(out.float().cpu())
         q.put((rank, outs, True))
         dist.barrier()
     except Exception as exc:
@@ -128,10 +144,9 @@ def _peer_worker(rank, world, port, q, fused=True):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", [True, False])
-def test_peer_store_ep_two_gpus(fused):
-    """Dispatch and combine as peer stores with on-device offsets (no host round trip); with
-    `fused` the down GEMM's epilogue itself performs the combine stores."""
+def test_peer_store_ep_two_gpus():
+    """Dispatch and combine as peer stores with on-device offsets and flags (no host round trip, no
+    collective); the down GEMM's epilogue itself performs the combine stores."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -140,7 +155,7 @@ def test_peer_store_ep_two_gpus(fused):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29800 + os.getpid() % 1000
-    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port + int(fused), q, fused)) for r in range(2)]
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(2)]
@@ -158,6 +173,13 @@ def test_peer_store_ep_two_gpus(fused):
         ref = orc.experts_forward_oracle(*[inp[k] for k in KEYS], cap, E, K)
         got = torch.cat([r[1][i] for r in results])
         orc.check_close(got, ref, 2e-2, f"peer-store expert parallel, call {i}", rel_l2=1e-2)
+    # the call after the overflow: 128 tokens per rank of the skewed 1024-token case
+    inp = workloads.make_inputs(1024, H, E, K, seed=10, weight_std=0.05, bias_std=0.1, dtype=torch.bfloat16, skew=True)
+    sel = torch.cat([torch.arange(0, 128), torch.arange(512, 640)])
+    ref = orc.experts_forward_oracle(inp["hidden_states"][sel], inp["router_indices"][sel],
+                                     inp["routing_weights"][sel], *[inp[k] for k in KEYS[3:]], 1024, E, K)
+    got = torch.cat([r[1][3] for r in results])
+    orc.check_close(got, ref, 2e-2, "peer-store expert parallel after an overflowing call", rel_l2=1e-2)
 
 
 PEER_BWD_CASES = ((1024, 1024, False, 9, True), (1024, 100, True, 10, False), (512, 512, True, 11, True))
@@ -189,6 +211,7 @@ def _peer_bwd_worker(rank, world, port, q):
             grads = ctx.backward(inp["grad_out"][lo:hi].cuda(), inp["hidden_states"][lo:hi].cuda(), ri, rw,
                                  *local_w, cap)
             torch.cuda.synchronize()
+            assert ctx.status() == 0, f"device status {ctx.status()}"
             outs.append((out.float().cpu(), [g.float().cpu() for g in grads]))
         q.put((rank, outs, True))
         dist.barrier()
@@ -235,3 +258,26 @@ def test_peer_store_ep_backward_two_gpus():
         for j, name in enumerate(["d_hidden", "d_routing", "d_wgu", "d_bgu", "d_wd", "d_bd"]):
             got_g = torch.cat([r[1][i][1][j] for r in results])
             orc.check_close(got_g, ref_g[j], 2e-2, f"peer-store backward {name}, call {i}", rel_l2=2e-2)
+
+
+def test_bounded_wait_gives_up_on_one_gpu():
+    """The one-warp wait of the expert-parallel path on flags nobody sets: with a 1 ms limit it must
+    return the time-out status and leave the GPU usable; with the flags set it must report 0."""
+    import ctypes
+    from yamoe_b200 import _lib
+    L = _lib.lib()
+    G = 4
+    flags = torch.zeros(G, dtype=torch.int32, device="cuda")
+    state = torch.zeros(64, dtype=torch.int32, device="cuda")
+    header = torch.zeros(16, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(L.yamoe_b200_ep_wait_probe(flags.data_ptr(), G, 3, 1_000_000, state.data_ptr(), header.data_ptr(), st),
+               "ep_wait_probe")
+    torch.cuda.synchronize()
+    assert int(header[4]) == 5 and int(state[0]) == 3
+    flags.fill_(3)
+    _lib.check(L.yamoe_b200_ep_wait_probe(flags.data_ptr(), G, 3, 1_000_000, state.data_ptr(), header.data_ptr(), st),
+               "ep_wait_probe")
+    torch.cuda.synchronize()
+    assert int(header[4]) == 0
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0      # the context still works

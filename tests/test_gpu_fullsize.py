@@ -113,3 +113,16 @@ def test_config5_backward_full_size():
     d_bd.index_add_(0, inp["router_indices"].reshape(-1),
                     (w.reshape(-1, 1) * inp["grad_out"].float().repeat_interleave(K, 0)))
     orc.check_close(grads[5].float().cpu(), d_bd, RTOL_BF16, "d_bd vs closed form", rel_l2=2e-2)
+    # weight gradients against the oracle at the full hidden size, for the fullest and the emptiest
+    # expert: the oracle runs on that expert's rows alone (a one-expert, top-1 problem)
+    counts = torch.bincount(inp["router_indices"].reshape(-1), minlength=E)
+    for e in (int(counts.argmax()), int(counts.argmin())):
+        tok = (inp["router_indices"] == e).any(1).nonzero().reshape(-1)
+        n = tok.numel()
+        one = orc.experts_backward_oracle(
+            inp["grad_out"][tok], inp["hidden_states"][tok], torch.zeros(n, 1, dtype=torch.int64),
+            inp["routing_weights"][tok, e].reshape(n, 1), inp["gate_up_proj"][e:e + 1], inp["gate_up_proj_bias"][e:e + 1],
+            inp["down_proj"][e:e + 1], inp["down_proj_bias"][e:e + 1], n, 1, 1)
+        for gi, name in ((2, "d_wgu"), (3, "d_bgu"), (4, "d_wd"), (5, "d_bd")):
+            orc.check_close(grads[gi][e].float().cpu(), one[gi][0], RTOL_BF16, f"{name}[{e}] vs oracle ({n} rows)",
+                            rel_l2=2e-2)

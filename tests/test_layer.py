@@ -60,6 +60,40 @@ def test_router_topk_kernel():
 
 
 @pytest.mark.gpu
+def test_router_topk_non_finite_logits():
+    """NaN rows and rows with fewer than K finite logits: every selected id must be a valid expert
+    and nothing may be written outside the [T, E] score row, as with torch.topk."""
+    import yamoe_b200
+    T, E, K = 6, 16, 4
+    logits = torch.randn(T, E, generator=torch.Generator().manual_seed(1))
+    logits[0] = float("nan")                       # a whole NaN row
+    logits[1, 3] = float("nan")                    # one NaN: ranks first, as in torch.topk
+    logits[2] = float("-inf"); logits[2, 5] = 1.0; logits[2, 9] = 0.5      # two finite logits, K = 4
+    logits[3] = float("-inf")                      # nothing finite at all
+    guard = torch.full((T * E + 64,), 7.0, device="cuda")
+    scores_buf = guard[:T * E].view(T, E)
+    from yamoe_b200 import _lib
+    idx = torch.full((T, K), -5, dtype=torch.int64, device="cuda")
+    _lib.check(_lib.lib().yamoe_b200_router_topk(logits.cuda().data_ptr(), idx.data_ptr(), scores_buf.data_ptr(), T, E, K,
+                                                 _lib.YAMOE_F32, torch.cuda.current_stream().cuda_stream), "router_topk")
+    torch.cuda.synchronize()
+    idx = idx.cpu()
+    assert ((idx >= 0) & (idx < E)).all(), idx
+    assert (guard[T * E:] == 7.0).all()            # nothing stored past the score rows
+    for t in range(T):
+        assert len(set(idx[t].tolist())) == K      # K distinct experts per row
+    assert idx[1, 0] == 3
+    assert set(idx[2, :2].tolist()) == {5, 9}
+    ref_v, ref_i = torch.topk(logits[4:], K, dim=-1)
+    assert torch.equal(idx[4:], ref_i)
+    ref = torch.zeros(2, E).scatter_(1, ref_i, torch.softmax(ref_v, -1))
+    assert (scores_buf[4:].cpu() - ref).abs().max() <= 1e-6
+    s2 = scores_buf[2].cpu()
+    assert abs(float(s2[5]) - float(torch.softmax(torch.tensor([1.0, 0.5]), 0)[0])) <= 1e-6
+    assert torch.isnan(scores_buf[0].cpu()[idx[0]]).all()
+
+
+@pytest.mark.gpu
 def test_yamoe_module_matches_reference_mlp():
     g, T, H, E, K = _golden_layer()
     m = _module(g, E, K, capacity=T)

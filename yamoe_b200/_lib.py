@@ -16,6 +16,19 @@ LIB_PATH = os.environ.get("YAMOE_B200_LIB") or _DEFAULT_LIB
 c_void_p, c_int, c_int64, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
 
 YAMOE_F32, YAMOE_BF16 = 0, 1
+
+
+class EpCtx(ctypes.Structure):
+    """yamoe_ep_ctx_t of include/yamoe_b200.h."""
+    _fields_ = ([(n, ctypes.c_int32) for n in ("G", "rank", "E", "K", "H", "dtype")] +
+                [("max_rows", ctypes.c_int64), ("back_rows", ctypes.c_int64)] +
+                [(n, ctypes.c_void_p) for n in ("peer_recv_x", "peer_recv_g", "peer_recv_w", "peer_back",
+                                                "peer_back_w", "peer_ctrl", "recv_x", "recv_g", "recv_w", "back",
+                                                "back_w", "ctrl", "state")] +
+                [("wait_ns", ctypes.c_uint64)])
+
+
+_ctx_p = ctypes.POINTER(EpCtx)
 PATH_AUTO, PATH_SIMT, PATH_TCGEN05, PATH_GEMV = 0, 1, 2, 3
 
 # name -> (restype, argtypes); mirrors include/yamoe_b200.h one to one
@@ -37,7 +50,7 @@ SIGNATURES = {
                                     [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_batch_mm_workspace_bytes": (c_size_t, [c_int, c_int]),
     "yamoe_b200_batch_mm": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_size_t, c_void_p]),
-    "yamoe_b200_permute_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "yamoe_b200_permute_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "yamoe_b200_combine_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                                         c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_ep_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
@@ -52,6 +65,14 @@ SIGNATURES = {
                                                c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "yamoe_b200_ep_local_backward": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int, c_int,
                                                                c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_ep_ctrl_bytes": (c_size_t, [c_int, c_int]),
+    "yamoe_b200_ep_call_workspace_bytes": (c_size_t, [_ctx_p, c_int64, c_int]),
+    "yamoe_b200_ep_forward": (c_int, [_ctx_p, c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 5 +
+                              [c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_ep_backward": (c_int, [_ctx_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 10 +
+                               [c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_ep_wait_probe": (c_int, [c_void_p, c_int, ctypes.c_int32, ctypes.c_uint64, c_void_p, c_void_p,
+                                         c_void_p]),
     "yamoe_b200_binned_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_int,
                                          c_int, c_void_p]),
     "yamoe_b200_binned_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
@@ -62,6 +83,7 @@ SIGNATURES = {
                                           [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_experts_backward_saved": (c_int, [c_void_p, c_int, c_void_p, c_int] + [c_void_p] * 9 +
                                           [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
+    "yamoe_b200_mbar_wait_probe": (c_int, [c_void_p, ctypes.c_uint64, c_void_p]),
     "yamoe_b200_device_status": (c_int, [c_void_p, c_void_p, ctypes.POINTER(ctypes.c_int32)]),
 }
 
@@ -81,6 +103,16 @@ def lib() -> ctypes.CDLL:
             fn.restype, fn.argtypes = res, args
         _lib = handle
     return _lib
+
+
+def check_device_status(workspace_ptr: int, stream: int, what: str) -> None:
+    """Reads the device status word at the head of a workspace (synchronises the stream) and raises
+    when a bounded device-side wait gave up during the call that used it."""
+    out = ctypes.c_int32(0)
+    check(lib().yamoe_b200_device_status(workspace_ptr, stream, ctypes.byref(out)), what + " (status read)")
+    if out.value != 0:
+        msg = lib().yamoe_b200_status_string(-6).decode()
+        raise RuntimeError(f"yamoe_b200: {what} failed: {msg} (device status {out.value})")
 
 
 def check(status: int, what: str) -> None:

@@ -121,20 +121,22 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 
 // Routing tables kept at the head of every workspace (all int32 unless noted).
 struct RouteTables {
-  int32_t* header;       // [16]: 0 ticket, 1 n_row_tiles, 2 rows_used, 3 dropped, 4 device status, 5 tile pairs
-  int32_t* counts;       // [E]
-  int32_t* bins;         // [E+1] inclusive prefix sums, bins[E] = 0
-  int32_t* pad_off;      // [E+1] first padded row of each expert, pad_off[E] = rows_used
-  int32_t* block_counts; // [nblk*E] per-block histogram, then exclusive prefix over blocks
-  int32_t* tile_expert;  // [max_row_tiles] expert owning each kTileM-row tile
-  int32_t* pair_off;     // [E+1] prefix sum of ceil(row tiles of e / 2): pairs of row tiles per expert
-  int32_t* pair_expert;  // [max_row_tiles] expert owning each pair of row tiles
-  int32_t* sorted_values;   // [S]
-  int32_t* sorted_indices;  // [S]
-  int32_t* row_token;    // [max_rows] token of each padded row, -1 for padding
-  int32_t* row_flat;     // [max_rows] flat position p = t*K + slot, -1 for padding
-  float* row_weight;     // [max_rows] routing weight of the row
-  int32_t* flat_row;     // [S] padded row of assignment p = t*K + slot, -1 when dropped
+  int32_t* header = nullptr;       // [16]: 0 ticket, 1 n_row_tiles, 2 rows_used, 3 dropped, 4 device status, 5 tile pairs
+  int32_t* counts = nullptr;       // [E]
+  int32_t* bins = nullptr;         // [E+1] inclusive prefix sums, bins[E] = 0
+  int32_t* pad_off = nullptr;      // [E+1] first padded row of each expert, pad_off[E] = rows_used
+  int32_t* block_counts = nullptr; // [nblk*E] per-block histogram, then exclusive prefix over blocks
+  int32_t* tile_expert = nullptr;  // [max_row_tiles] expert owning each kTileM-row tile
+  int32_t* pair_off = nullptr;     // [E+1] prefix sum of ceil(row tiles of e / 2): pairs of row tiles per expert
+  int32_t* pair_expert = nullptr;  // [max_row_tiles] expert owning each pair of row tiles
+  int32_t* sorted_values = nullptr;   // [S]
+  int32_t* sorted_indices = nullptr;  // [S]
+  int32_t* row_token = nullptr;    // [max_rows] token of each padded row, -1 for padding
+  int32_t* row_flat = nullptr;     // [max_rows] flat position p = t*K + slot, -1 for padding
+  float* row_weight = nullptr;     // [max_rows] routing weight of the row
+  int32_t* flat_row = nullptr;     // [S] padded row of assignment p = t*K + slot, -1 when dropped
+  int32_t* flat_pos = nullptr;     // [S] optional: position of assignment p in the sorted order (inverse of
+                                   //     sorted_indices); the caller pre-fills it with -1
 };
 
 enum HeaderSlot { kHdrTicket = 0, kHdrRowTiles = 1, kHdrRowsUsed = 2, kHdrDropped = 3, kHdrStatus = 4, kHdrPairs = 5 };

@@ -1,0 +1,357 @@
+// Expert parallelism without host-side collectives: the count exchange and the two phase
+// boundaries of the peer-store path (ep_p2p.cuh) become flags in symmetric memory, so that one
+// expert-parallel call is a fixed chain of kernels on one stream and no NCCL call at all.
+// The reference is single-GPU; there is no counterpart.
+//
+// Every rank owns a control block that its peers may write (EpCtrl, layout below).  A call has an
+// epoch number (a device counter in the rank's private state, incremented by the first kernel of
+// the call).  Flags carry the epoch of the phase that completed:
+//
+//   ep_publish_kernel     my per-expert counts -> counts[epoch & 1][rank][:] of every peer, then
+//                         flag_counts[rank] = epoch there
+//   ep_dispatch_kernel    waits until flag_counts[s] >= epoch for every source s (bounded), derives
+//                         every offset from the [G, E] counts (as ep_plan_kernel does), stores my
+//                         rows into the owners' receive buffers, and its last CTA sets
+//                         flag_dispatch[rank] = epoch on every peer
+//   ep_wait_kernel        one warp; waits for flag_dispatch[s] >= epoch from every source (bounded)
+//   (grouped GEMMs; the last one returns result rows to their sources from its epilogue)
+//   ep_signal_kernel      flag_return[rank] = epoch on every peer
+//   ep_combine_kernel     waits for flag_return[o] >= epoch from every owner (bounded), then sums
+//                         each token's K returned rows
+//
+// Only stores cross NVLink; every wait polls this GPU's own memory with ld.acquire.sys and gives
+// up after `wait_ns`, recording a status word in the workspace header (the data of that call is
+// then invalid, the GPU and all buffers stay usable).  A rank reuses a peer's buffer only after
+// that peer told it, by the flags of the previous phase, that it is done reading: the receive
+// buffers are written in call n+1 only after every owner signalled flag_return for call n, which
+// it does after its last kernel that reads them; the back buffers only after the token owner
+// signalled flag_dispatch for call n+1, which follows its combine of call n on its stream.
+//
+// Rows whose destination would fall outside the receive buffer are never stored: the plan checks
+// every owner's padded row total against max_rows and, on overflow, marks the call invalid on
+// every rank (all ranks see the same counts) so that nothing is stored or computed.
+#pragma once
+#include "common.cuh"
+#include "ep_p2p.cuh"
+#include "misc_kernels.cuh"
+
+namespace yb {
+
+enum EpStatus {
+  kStatusEpCountsTimeout = 4,
+  kStatusEpDispatchTimeout = 5,
+  kStatusEpReturnTimeout = 6,
+  kStatusEpOverflow = 7,
+};
+
+// Layout (int32 words) of the control block peers write into.
+struct EpCtrlLayout {
+  int G, E;
+  __host__ __device__ int counts(int parity, int src) const { return (parity * G + src) * E; }
+  __host__ __device__ int flag_counts() const { return 2 * G * E; }
+  __host__ __device__ int flag_dispatch() const { return 2 * G * E + 64 * ((G + 63) / 64); }
+  __host__ __device__ int flag_return() const { return 2 * G * E + 2 * 64 * ((G + 63) / 64); }
+  __host__ __device__ int words() const { return 2 * G * E + 3 * 64 * ((G + 63) / 64); }
+};
+
+// Private per-rank state that lives across calls (zeroed once by the owner).
+enum EpStateSlot { kEpStateEpoch = 0, kEpStateTicket = 1 };
+
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ep_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Polls a flag in this GPU's memory until it reaches `epoch`; false when `limit_ns` ran out.
+__device__ __forceinline__ bool ep_wait_flag(const int32_t* flag, int32_t epoch, uint64_t limit_ns) {
+  const uint64_t t0 = ep_timer_ns();
+  for (;;) {
+    if (ld_acquire_sys(flag) - epoch >= 0) return true;
+    if (ep_timer_ns() - t0 > limit_ns) return false;
+    __nanosleep(64);
+  }
+}
+
+// One CTA.  Starts a call: bumps the epoch, then tells every rank how many assignments this rank
+// has for each expert.
+__global__ void __launch_bounds__(256)
+ep_publish_kernel(const int32_t* __restrict__ counts, int32_t* __restrict__ state, void* const* __restrict__ peer_ctrl,
+                  EpCtrlLayout lay, int rank) {
+  __shared__ int32_t s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = state[kEpStateEpoch] + 1;
+    state[kEpStateEpoch] = s_epoch;
+    state[kEpStateTicket] = 0;
+  }
+  __syncthreads();
+  const int32_t epoch = s_epoch;
+  for (int i = threadIdx.x; i < lay.G * lay.E; i += blockDim.x) {
+    const int g = i / lay.E, e = i - g * lay.E;
+    reinterpret_cast<int32_t*>(peer_ctrl[g])[lay.counts(epoch & 1, rank) + e] = counts[e];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < lay.G)
+    st_release_sys(reinterpret_cast<int32_t*>(peer_ctrl[threadIdx.x]) + lay.flag_counts() + rank, epoch);
+}
+
+struct EpDispatchArgs {
+  const void* hidden;            // [T, H]
+  const void* grad;              // [T, H] or null          (backward: upstream-gradient rows)
+  const void* routing_weights;   // [T, routing_cols] or null (backward: one fp32 per row travels)
+  int routing_cols;
+  const int32_t* sorted_values;  // [S]
+  const int32_t* sorted_indices; // [S]
+  const int32_t* bins;           // [E+1]
+  void* const* peer_x;           // [G] receive buffers for token rows
+  void* const* peer_g;           // [G] receive buffers for gradient rows, or null
+  void* const* peer_w;           // [G] receive buffers for routing weights, or null
+  void* const* peer_ctrl;        // [G]
+  const int32_t* ctrl;           // this rank's control block
+  int32_t* state;
+  int64_t max_rows;
+  int S, H, E, G, rank, K;
+  uint64_t wait_ns;
+};
+
+// Persistent grid.  Shared memory: 3*E + 2 int32.
+template <typename T>
+__global__ void __launch_bounds__(kRowWarps * 32)
+ep_dispatch_fused_kernel(const EpDispatchArgs a, EpTables t) {
+  extern __shared__ int32_t sm[];
+  int32_t* tot = sm;               // [E] rows of expert e over all sources
+  int32_t* before = sm + a.E;      // [E] rows of expert e from sources s < rank
+  int32_t* poff = sm + 2 * a.E;    // [E] padded row offset of e inside its owner
+  __shared__ int s_bad, s_last;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int E = a.E, G = a.G, per = E / G, rank = a.rank;
+  const EpCtrlLayout lay{G, E};
+  const int32_t epoch = a.state[kEpStateEpoch];
+  if (tid == 0) s_bad = 0;
+  __syncthreads();
+  // ---- every source's counts for this call must have arrived ---------------------------------
+  if (tid < G && !ep_wait_flag(a.ctrl + lay.flag_counts() + tid, epoch, a.wait_ns)) {
+    s_bad = kStatusEpCountsTimeout;
+  }
+  __syncthreads();
+  const int32_t* counts_all = a.ctrl + lay.counts(epoch & 1, 0);   // [G][E]
+  if (s_bad == 0) {
+    for (int e = tid; e < E; e += nthr) {
+      int c_all = 0, c_before = 0;
+      for (int s = 0; s < G; ++s) {
+        const int c = max(__ldcg(counts_all + s * E + e), 0);
+        if (s < rank) c_before += c;
+        c_all += c;
+      }
+      tot[e] = c_all;
+      before[e] = c_before;
+    }
+    __syncthreads();
+    if (tid < G) {                  // padded offsets inside owner `tid`, checked against the buffer
+      int64_t rows = 0;
+      for (int le = 0; le < per; ++le) {
+        const int e = tid * per + le;
+        poff[e] = (int)rows;
+        rows += (tot[e] + kTileM - 1) / kTileM * kTileM;
+        if (rows > a.max_rows) { s_bad = kStatusEpOverflow; break; }
+      }
+    }
+    __syncthreads();
+  }
+  const int bad = s_bad;
+  // ---- CTA 0: this rank's own tables (what ep_plan_kernel writes) -------------------------------
+  if (blockIdx.x == 0) {
+    if (bad != 0) {
+      if (tid == 0) {
+        atomicMax(t.rt.header + kHdrStatus, bad);
+        t.rt.header[kHdrRowTiles] = 0;
+        t.rt.header[kHdrRowsUsed] = 0;
+        t.rt.header[kHdrPairs] = 0;
+        t.rt.header[kHdrDropped] = 0;
+      }
+      for (int le = tid; le <= per; le += nthr) {
+        t.rt.pad_off[le] = 0;
+        t.rt.pair_off[le] = 0;
+        t.rt.bins[le] = 0;
+        if (le < per) t.rt.counts[le] = 0;
+      }
+    } else {
+      for (int i = tid; i < G * per; i += nthr) {
+        const int s = i / per, le = i - s * per, e = rank * per + le;
+        int start = 0;
+        for (int e2 = 0; e2 < e; ++e2) start += max(__ldcg(counts_all + s * E + e2), 0);
+        int row = poff[e];
+        for (int s2 = 0; s2 < s; ++s2) row += max(__ldcg(counts_all + s2 * E + e), 0);
+        t.src_start[i] = start;
+        t.seg_row[i] = row;
+      }
+      if (tid == 0) {
+        int rows = 0, pairs = 0, cum = 0;
+        for (int le = 0; le < per; ++le) {
+          const int c = tot[rank * per + le];
+          cum += c;
+          t.rt.counts[le] = c;
+          t.rt.bins[le] = cum;
+          t.rt.pad_off[le] = rows;
+          t.rt.pair_off[le] = pairs;
+          const int tiles = (c + kTileM - 1) / kTileM;
+          for (int k = 0; k < tiles; ++k) t.rt.tile_expert[rows / kTileM + k] = le;
+          for (int k = 0; k < (tiles + 1) / 2; ++k) t.rt.pair_expert[pairs + k] = le;
+          rows += tiles * kTileM;
+          pairs += (tiles + 1) / 2;
+        }
+        t.rt.bins[per] = 0;
+        t.rt.pad_off[per] = rows;
+        t.rt.pair_off[per] = pairs;
+        t.rt.header[kHdrRowTiles] = rows / kTileM;
+        t.rt.header[kHdrRowsUsed] = rows;
+        t.rt.header[kHdrPairs] = pairs;
+        t.rt.header[kHdrDropped] = 0;
+      }
+    }
+  }
+  // ---- my rows -> their owners -------------------------------------------------------------------
+  if (bad == 0) {
+    const int warp = tid >> 5, lane = tid & 31;
+    const int n_valid = a.bins[E - 1];
+    // start with the rows of the next rank's experts, so that the G sources do not all begin with
+    // owner 0: at any moment every owner receives from a different source
+    const int first_e = ((rank + 1) % G) * per;
+    const int rot = first_e ? a.bins[first_e - 1] : 0;
+    const int nvec = a.H * (int)sizeof(T) / 16;
+    for (int jj = blockIdx.x * kRowWarps + warp; jj < n_valid; jj += gridDim.x * kRowWarps) {
+      int j = jj + rot;
+      if (j >= n_valid) j -= n_valid;
+      const int e = a.sorted_values[j];
+      const int i = j - (e ? a.bins[e - 1] : 0);
+      const int flat = a.sorted_indices[j];
+      const int tok = flat / a.K;
+      const int owner = e / per;
+      const int64_t drow = (int64_t)poff[e] + before[e] + i;
+      if (drow >= a.max_rows) continue;          // cannot happen once the totals passed the check
+      {
+        const uint4* s = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.hidden) + (size_t)tok * a.H);
+        uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.peer_x[owner]) + (size_t)drow * a.H);
+        for (int v = lane; v < nvec; v += 32) d[v] = __ldg(s + v);
+      }
+      if (a.grad != nullptr) {
+        const uint4* s = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.grad) + (size_t)tok * a.H);
+        uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.peer_g[owner]) + (size_t)drow * a.H);
+        for (int v = lane; v < nvec; v += 32) d[v] = __ldg(s + v);
+      }
+      if (a.routing_weights != nullptr && lane == 0) {
+        const size_t idx = a.routing_cols == E ? (size_t)tok * E + e : (size_t)flat;
+        reinterpret_cast<float*>(a.peer_w[owner])[drow] =
+            DT<T>::ld(reinterpret_cast<const T*>(a.routing_weights) + idx);
+      }
+    }
+  }
+  // ---- the last CTA tells every owner that this rank's rows are in place -----------------------
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) s_last = (atomicAdd(a.state + kEpStateTicket, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (tid < G)
+      st_release_sys(reinterpret_cast<int32_t*>(a.peer_ctrl[tid]) + lay.flag_dispatch() + rank, epoch);
+    if (tid == 0) a.state[kEpStateTicket] = 0;
+  }
+}
+
+// One warp: lane s waits for `flags[s]` to reach the epoch of this call.
+__global__ void ep_wait_kernel(const int32_t* __restrict__ flags, int G, const int32_t* __restrict__ state,
+                               int32_t* __restrict__ header, int status_code, uint64_t wait_ns) {
+  const int32_t epoch = state[kEpStateEpoch];
+  for (int s = threadIdx.x; s < G; s += blockDim.x)
+    if (!ep_wait_flag(flags + s, epoch, wait_ns)) atomicMax(header + kHdrStatus, status_code);
+}
+
+// One warp: everything this rank stored into its peers during the preceding kernels of the stream
+// is made visible, then flag[rank] = epoch on every peer.
+__global__ void ep_signal_kernel(void* const* __restrict__ peer_ctrl, int flag_word, int G, int rank,
+                                 const int32_t* __restrict__ state) {
+  const int32_t epoch = state[kEpStateEpoch];
+  __threadfence_system();
+  for (int g = threadIdx.x; g < G; g += blockDim.x)
+    st_release_sys(reinterpret_cast<int32_t*>(peer_ctrl[g]) + flag_word + rank, epoch);
+}
+
+// out[t, :] = sum_k w[t, k] * back[flat_pos[t*K + k], :] once every owner's rows have come back.
+// `back` was written by other GPUs while this kernel may already have been running: it is read
+// with L1 bypassed.  UNIT: weights are 1 (the backward pass returns already-weighted rows).
+template <typename T, bool UNIT>
+__global__ void __launch_bounds__(kRowWarps * 32)
+ep_combine_kernel(const T* __restrict__ back, const int32_t* __restrict__ flat_pos,
+                  const int64_t* __restrict__ router_indices, const T* __restrict__ routing_weights,
+                  int routing_cols, T* __restrict__ out, int64_t Tn, int H, int E, int K,
+                  const int32_t* __restrict__ flags, int G, const int32_t* __restrict__ state,
+                  int32_t* __restrict__ header, uint64_t wait_ns) {
+  const int32_t epoch = state[kEpStateEpoch];
+  if (threadIdx.x < G && !ep_wait_flag(flags + threadIdx.x, epoch, wait_ns))
+    atomicMax(header + kHdrStatus, (int)kStatusEpReturnTimeout);
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  constexpr int VE = 16 / (int)sizeof(T);
+  const int nvec = H / VE;
+  for (int64_t t = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5); t < Tn; t += (int64_t)gridDim.x * kRowWarps) {
+    for (int i = lane; i < nvec; i += 32) {
+      float acc[VE];
+#pragma unroll
+      for (int j = 0; j < VE; ++j) acc[j] = 0.f;
+      for (int k = 0; k < K; ++k) {
+        const int32_t r = flat_pos[t * K + k];
+        if (r < 0) continue;
+        float w = 1.0f;
+        if constexpr (!UNIT) {
+          const int col = (routing_cols == E) ? (int)router_indices[t * K + k] : k;
+          w = DT<T>::ld(routing_weights + (size_t)t * routing_cols + col);
+        }
+        const uint4 q = __ldcg(reinterpret_cast<const uint4*>(back + (size_t)r * H) + i);
+        float v[VE];
+        if constexpr (sizeof(T) == 2) {
+          const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[2 * j] = __uint_as_float(u[j] << 16);
+            v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+          }
+        } else {
+          v[0] = __uint_as_float(q.x); v[1] = __uint_as_float(q.y);
+          v[2] = __uint_as_float(q.z); v[3] = __uint_as_float(q.w);
+        }
+#pragma unroll
+        for (int j = 0; j < VE; ++j) acc[j] = fmaf(w, v[j], acc[j]);
+      }
+      store_vec<T, VE>(out + (size_t)t * H + (size_t)i * VE, acc);
+    }
+  }
+}
+
+// d_routing[t, expert] (dense) or d_routing[t, slot] = returned routing-weight gradient of the
+// assignment, 0 for assignments that were not routed.  `d_routing` must be zero-filled when dense.
+template <typename T>
+__global__ void ep_routing_grad_kernel(const float* __restrict__ back_w, const int32_t* __restrict__ flat_pos,
+                                       const int64_t* __restrict__ router_indices, T* __restrict__ d_routing,
+                                       int64_t S, int routing_cols, int E, int K) {
+  const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= S) return;
+  const int32_t j = flat_pos[p];
+  const float v = j >= 0 ? __ldcg(back_w + j) : 0.f;
+  if (routing_cols == E) {
+    const int64_t e = router_indices[p];
+    if (e >= 0 && e < E && j >= 0) DT<T>::st(d_routing + (p / K) * E + e, v);
+  } else {
+    DT<T>::st(d_routing + p, v);
+  }
+}
+
+}  // namespace yb

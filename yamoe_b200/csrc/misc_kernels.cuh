@@ -195,21 +195,28 @@ combine_padded_kernel(const T* __restrict__ y, const int32_t* __restrict__ flat_
 template <typename T>
 __global__ void __launch_bounds__(kRowWarps * 32)
 permute_rows_kernel(const T* __restrict__ src, const int32_t* __restrict__ sorted_indices, T* __restrict__ dst,
-                    int64_t S, int H, int K) {
+                    int64_t S, int H, int K, int64_t n_src) {
   const int64_t row = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   if (row >= S) return;
   const int lane = threadIdx.x & 31;
-  const int tok = sorted_indices[row] / K;
+  const int flat = sorted_indices[row];
   const int nvec = H * (int)sizeof(T) / 16;
-  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)tok * H);
   uint4* d = reinterpret_cast<uint4*>(dst + (size_t)row * H);
+  if (flat < 0 || flat / K >= n_src) {          // entry of a dropped assignment (-1): a zero row
+    for (int i = lane; i < nvec; i += 32) d[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)(flat / K) * H);
   for (int i = lane; i < nvec; i += 32) d[i] = __ldg(s + i);
 }
 
-// inv[sorted_indices[j]] = j
-__global__ void invert_perm_kernel(const int32_t* __restrict__ sorted_indices, int32_t* __restrict__ inv, int64_t S) {
+// inv[sorted_indices[j]] = j; entries outside [0, n_flat) (the -1 tail left for dropped assignments) are skipped
+__global__ void invert_perm_kernel(const int32_t* __restrict__ sorted_indices, int32_t* __restrict__ inv, int64_t S,
+                                   int64_t n_flat) {
   const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (j < S) inv[sorted_indices[j]] = (int32_t)j;
+  if (j >= S) return;
+  const int32_t p = sorted_indices[j];
+  if (p >= 0 && p < n_flat) inv[p] = (int32_t)j;
 }
 
 // out[t, :] = sum_k w[t, k] * rows[inv[t*K + k], :]   (fp32 accumulation, fixed order, one rounding).

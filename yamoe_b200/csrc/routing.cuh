@@ -157,6 +157,7 @@ route_place_kernel(const int64_t* __restrict__ router_indices, const T* __restri
       const int start = e ? rt.bins[e - 1] : 0;
       rt.sorted_values[start + pos] = e;
       rt.sorted_indices[start + pos] = p;
+      if (rt.flat_pos != nullptr) rt.flat_pos[p] = start + pos;
       if (rt.row_token != nullptr && (int64_t)pos < capacity) {
         const int r = rt.pad_off[e] + pos;
         const int t = p / K;

@@ -14,6 +14,12 @@
 // main loop of tile i+1.  Tiles are walked expert by expert with the row tile varying fastest,
 // so the CTAs running at any moment share one expert's weight slab in L2.
 //
+// Tile look-up is kept off the critical path: the padded row offsets of all experts sit in
+// shared memory, and the one table entry a tile still needs from global memory (its expert) is
+// fetched one tile ahead, so that no role stalls on a dependent global load between two tiles.
+// The last column tile of a matrix whose width is not a multiple of BN is issued with a narrower
+// instruction (N = remaining columns) and loads only the boxes it needs.
+//
 // Every mbarrier wait is bounded: after kWaitLimitNs the waiting role raises an abort flag,
 // all roles leave their loops, the CTA frees its TMEM, records a status code in the workspace
 // header and returns.
@@ -32,7 +38,21 @@ constexpr int kUmmaBM = 128;
 constexpr int kUmmaBK = 64;            // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaThreads = 192;
 constexpr int kUmmaAccStride = 256;    // TMEM columns between the two accumulators
+constexpr int kUmmaMaxExperts = 1024;  // padded row offsets of up to this many experts are cached in shared memory
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+// Optional wait-time accounting for pipeline studies (compile with -DYB_PROF): every role adds the
+// SM clocks it spent inside bounded waits to g_prof[slot]; yamoe_b200_prof_read returns and clears them.
+#ifdef YB_PROF
+__device__ unsigned long long g_prof[16];
+#define YB_PROF_T0 const long long _pt0 = clock64();
+#define YB_PROF_ADD(var) var += clock64() - _pt0;
+#define YB_PROF_FLUSH(slot, var) atomicAdd(&g_prof[slot], (unsigned long long)(var));
+#else
+#define YB_PROF_T0
+#define YB_PROF_ADD(var)
+#define YB_PROF_FLUSH(slot, var)
+#endif
 
 enum DeviceStatus { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusMmaTimeout = 2, kStatusEpilogueTimeout = 3 };
 
@@ -65,16 +85,34 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 // Bounded wait on an mbarrier phase.  Returns false when the wait was abandoned.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      if (*abort_flag != 0 || now - t0 > kWaitLimitNs) return false;
+      if (*abort_flag != 0 || now - t0 > limit_ns) return false;
     }
   }
+}
+
+// Test aid: one thread waits, with the given limit, on a barrier that nothing ever arrives at,
+// and records what the grouped GEMM's roles record when a wait gives up.  No TMA, no TMEM.
+__global__ void mbar_wait_probe_kernel(int32_t* header, uint64_t limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!mbar_wait(smem_u32(&bar), 0, &abort_flag, limit_ns)) {
+      abort_flag = 1;
+      atomicMax(header + kHdrStatus, (int)kStatusProducerTimeout);
+    }
+  }
+  __syncthreads();
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
@@ -158,7 +196,7 @@ struct UmmaSmem {
   static constexpr int kABytes = kUmmaBM * 128;
   static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (227 * 1024 - 2048) / kStageBytes;  // 7 / 5 / 4 stages for BN 128 / 192 / 256
+  static constexpr int kStages = (227 * 1024 - 8192) / kStageBytes;  // 6 / 5 / 4 stages for BN 128 / 192 / 256
   static constexpr int kTotal = kStages * kStageBytes + 1024;       // + slack for 1024-byte alignment
 };
 
@@ -175,6 +213,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int32_t s_pad[kUmmaMaxExperts + 1];   // copy of pad_off[0..E]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -204,6 +243,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // previous kernel has completed before touching anything it produced.
   pdl_trigger();
   pdl_wait();
+  const bool pad_in_smem = p.E <= kUmmaMaxExperts;
+  if (pad_in_smem) {
+    for (int i = threadIdx.x; i <= p.E; i += kUmmaThreads) s_pad[i] = p.pad_off[i];
+    __syncthreads();
+  }
+  const int32_t* pad = pad_in_smem ? s_pad : p.pad_off;
 
   // ---- tile walk (identical in every role) ---------------------------------------------------
   const int NT = (p.N + BN - 1) / BN;
@@ -215,20 +260,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     total = p.header[kHdrRowTiles] * NT;
   }
-  auto decode = [&](int id, int& e, int& row0, int& n0, int& kb_begin_row, int& kblocks) {
+  // Expert of tile `id` for the row-tiled arrangements: the only part of a tile's description
+  // that comes from global memory.  Every role asks for it one tile ahead.
+  auto expert_of = [&](int id) -> int {
+    if constexpr (MODE == kWgrad) return 0;
+    return id < total ? __ldg(p.tile_expert + id / NT) : 0;
+  };
+  auto decode = [&](int id, int e_hint, int& e, int& row0, int& n0, int& kb_begin_row, int& kblocks) {
     if constexpr (MODE == kWgrad) {
       e = id / (MT * NT);
       const int rem = id - e * (MT * NT);
       const int nt = rem / MT;
       row0 = (rem - nt * MT) * kUmmaBM;
       n0 = nt * BN;
-      kb_begin_row = p.pad_off[e];
-      kblocks = (p.pad_off[e + 1] - kb_begin_row) / kUmmaBK;
+      kb_begin_row = pad[e];
+      kblocks = (pad[e + 1] - kb_begin_row) / kUmmaBK;
     } else {
-      const int u = id / NT;
-      e = p.tile_expert[u];
-      const int first = p.pad_off[e] / kTileM;
-      const int cnt = (p.pad_off[e + 1] - p.pad_off[e]) / kTileM;
+      e = e_hint;
+      const int p0 = pad[e];
+      const int first = p0 / kTileM;
+      const int cnt = (pad[e + 1] - p0) / kTileM;
       const int local = id - first * NT;
       const int nt = local / cnt;
       row0 = (first + (local - nt * cnt)) * kUmmaBM;
@@ -247,9 +298,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int e_next = expert_of(blockIdx.x);
       for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
         int e, row0, n0, krow, kblocks;
-        decode(id, e, row0, n0, krow, kblocks);
+        decode(id, e_next, e, row0, n0, krow, kblocks);
+        e_next = expert_of(id + gridDim.x);
+        const int nboxes = (min(BN, p.N - n0) + 63) >> 6;
         int4 r = *reinterpret_cast<const int4*>(p.gather_rows + row0 + 4 * lane);
         r.x = max(r.x, 0); r.y = max(r.y, 0); r.z = max(r.z, 0); r.w = max(r.w, 0);   // padding rows: any valid row
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -268,9 +322,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sa = smem_base + stage * SM::kStageBytes;
           const uint32_t sb = sa + SM::kABytes;
           if (lane == 0) {
-            mbar_expect_tx(full, SM::kStageBytes);
+            mbar_expect_tx(full, SM::kABytes + nboxes * 8192);
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i) tma_load_3d(sb + i * 8192, &tmB, n0 + i * 64, kb * kUmmaBK, e, full);
+            for (int i = 0; i < BN / 64; ++i)
+              if (i < nboxes) tma_load_3d(sb + i * 8192, &tmB, n0 + i * 64, kb * kUmmaBK, e, full);
           }
           __syncwarp();
           tma_gather4(sa + lane * 512, &tmA, kb * kUmmaBK, r.x, r.y, r.z, r.w, full);
@@ -281,31 +336,43 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long prof_empty = 0;
+      (void)prof_empty;
+      int e_next = expert_of(blockIdx.x);
       for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
         int e, row0, n0, krow, kblocks;
-        decode(id, e, row0, n0, krow, kblocks);
+        decode(id, e_next, e, row0, n0, krow, kblocks);
+        e_next = expert_of(id + gridDim.x);      // consumed after this tile's k loop
+        // MN-major B arrives as 64-column boxes: the last column tile asks only for those it has.
+        // (The K-major B of the data gradients is one box of BN rows; rows past N read as zeros.)
+        const int nboxes = MODE == kDgrad ? BN / 64 : (min(BN, p.N - n0) + 63) >> 6;
+        const uint32_t stage_tx = SM::kABytes + nboxes * 8192;
         for (int kb = 0; kb < kblocks; ++kb) {
+          YB_PROF_T0
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
             abort_flag = 1;
             atomicMax(p.header + kHdrStatus, (int)kStatusProducerTimeout);
             ok = false;
             break;
           }
+          YB_PROF_ADD(prof_empty)
           const uint32_t full = smem_u32(&bar_full[stage]);
           const uint32_t sa = smem_base + stage * SM::kStageBytes;
           const uint32_t sb = sa + SM::kABytes;
-          mbar_expect_tx(full, SM::kStageBytes);
+          mbar_expect_tx(full, stage_tx);
           if constexpr (MODE == kWgrad) {
             const int r = krow + kb * kUmmaBK;
 #pragma unroll
             for (int i = 0; i < kUmmaBM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, row0 + i * 64, r, full);
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmB, n0 + i * 64, r, full);
+            for (int i = 0; i < BN / 64; ++i)
+              if (i < nboxes) tma_load_2d(sb + i * 8192, &tmB, n0 + i * 64, r, full);
           } else {
             tma_load_2d(sa, &tmA, kb * kUmmaBK, row0, full);
             if constexpr (MODE == kFwd) {
 #pragma unroll
-              for (int i = 0; i < BN / 64; ++i) tma_load_3d(sb + i * 8192, &tmB, n0 + i * 64, kb * kUmmaBK, e, full);
+              for (int i = 0; i < BN / 64; ++i)
+                if (i < nboxes) tma_load_3d(sb + i * 8192, &tmB, n0 + i * 64, kb * kUmmaBK, e, full);
             } else {
               tma_load_3d(sb, &tmB, kb * kUmmaBK, n0, e, full);
             }
@@ -313,6 +380,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (++stage == kUmmaStages) { stage = 0; phase ^= 1u; }
         }
       }
+      YB_PROF_FLUSH(0, prof_empty)
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -320,31 +388,49 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       constexpr bool kAMn = (MODE == kWgrad);
       constexpr bool kBMn = (MODE != kDgrad);
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kAMn ? 1u : 0u) << 15) |
-                                 ((kBMn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
-                                 ((uint32_t)(kUmmaBM >> 4) << 24);
+      // instruction descriptor without its N field (bits 17..22 = N / 8), which depends on the tile
+      constexpr uint32_t idesc_base = (1u << 4) | (1u << 7) | (1u << 10) | ((kAMn ? 1u : 0u) << 15) |
+                                      ((kBMn ? 1u : 0u) << 16) | ((uint32_t)(kUmmaBM >> 4) << 24);
       constexpr uint32_t a_kstep = kAMn ? (16 * 128) >> 4 : 32 >> 4;   // descriptor units of 16 bytes
       constexpr uint32_t b_kstep = kBMn ? (16 * 128) >> 4 : 32 >> 4;
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      long long prof_full = 0, prof_tmem = 0, prof_all = 0;
+      (void)prof_full; (void)prof_tmem; (void)prof_all;
+#ifdef YB_PROF
+      const long long prof_begin = clock64();
+#endif
+      int e_next = expert_of(blockIdx.x);
       for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
         int e, row0, n0, krow, kblocks;
-        decode(id, e, row0, n0, krow, kblocks);
+        decode(id, e_next, e, row0, n0, krow, kblocks);
+        e_next = expert_of(id + gridDim.x);
         if (kblocks == 0) continue;
-        if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
-          abort_flag = 1;
-          atomicMax(p.header + kHdrStatus, (int)kStatusMmaTimeout);
-          break;
+        // columns this tile really has, rounded up to the instruction's granularity of 16
+        const uint32_t ncols = (uint32_t)(min(BN, p.N - n0) + 15) & ~15u;
+        const uint32_t idesc = idesc_base | ((ncols >> 3) << 17);
+        {
+          YB_PROF_T0
+          if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) {
+            abort_flag = 1;
+            atomicMax(p.header + kHdrStatus, (int)kStatusMmaTimeout);
+            break;
+          }
+          YB_PROF_ADD(prof_tmem)
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kUmmaAccStride;
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
-            abort_flag = 1;
-            atomicMax(p.header + kHdrStatus, (int)kStatusMmaTimeout);
-            ok = false;
-            break;
+          {
+            YB_PROF_T0
+            if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) {
+              abort_flag = 1;
+              atomicMax(p.header + kHdrStatus, (int)kStatusMmaTimeout);
+              ok = false;
+              break;
+            }
+            YB_PROF_ADD(prof_full)
           }
           tc_fence_after();
           const uint32_t sa = smem_base + stage * SM::kStageBytes;
@@ -363,6 +449,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
+#ifdef YB_PROF
+      prof_all = clock64() - prof_begin;
+#endif
+      YB_PROF_FLUSH(2, prof_full)
+      YB_PROF_FLUSH(3, prof_tmem)
+      YB_PROF_FLUSH(4, prof_all)
     }
     __syncwarp();
   } else {
@@ -370,9 +462,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;                    // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
+    int e_next = expert_of(blockIdx.x);
     for (int id = blockIdx.x; id < total; id += gridDim.x) {
       int e, row0, n0, krow, kblocks;
-      decode(id, e, row0, n0, krow, kblocks);
+      decode(id, e_next, e, row0, n0, krow, kblocks);
+      e_next = expert_of(id + gridDim.x);
       const int row = row0 + q * 32 + lane;
       if (kblocks == 0) {
         float z[32];

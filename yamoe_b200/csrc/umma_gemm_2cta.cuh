@@ -82,6 +82,8 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];         // used in the leader CTA
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int32_t s_pad[kUmmaMaxExperts + 1];    // copy of pad_off[0..E]
+  __shared__ int32_t s_pair[kUmmaMaxExperts + 1];   // copy of pair_off[0..E]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -110,20 +112,33 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   cluster_sync_all();          // the peer's barriers exist before any remote signal is sent
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  // Tile look-up off the critical path, as in the one-CTA kernel: offset tables in shared memory,
+  // the expert of a work item fetched one item ahead.
+  const bool tab_in_smem = p.E <= kUmmaMaxExperts;
+  if (tab_in_smem) {
+    for (int i = threadIdx.x; i <= p.E; i += kU2Threads) {
+      s_pad[i] = p.pad_off[i];
+      s_pair[i] = p.pair_off[i];
+    }
+    __syncthreads();
+  }
+  const int32_t* pad = tab_in_smem ? s_pad : p.pad_off;
+  const int32_t* pair = tab_in_smem ? s_pair : p.pair_off;
 
   const int NT = (p.N + BN - 1) / BN;
   const int total = p.header[kHdrPairs] * NT;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-  auto decode = [&](int id, int& e, int& row0, bool& has1, int& n0) {
-    const int u = id / NT;
-    e = p.pair_expert[u];
-    const int first = p.pair_off[e];
-    const int cnt = p.pair_off[e + 1] - first;
+  auto expert_of = [&](int id) -> int { return id < total ? __ldg(p.pair_expert + id / NT) : 0; };
+  auto decode = [&](int id, int e_hint, int& e, int& row0, bool& has1, int& n0) {
+    e = e_hint;
+    const int first = pair[e];
+    const int cnt = pair[e + 1] - first;
     const int local = id - first * NT;
     const int nt = local / cnt;
     const int pl = local - nt * cnt;
-    const int tiles = (p.pad_off[e + 1] - p.pad_off[e]) / kTileM;
-    row0 = p.pad_off[e] + pl * 256;
+    const int p0 = pad[e];
+    const int tiles = (pad[e + 1] - p0) / kTileM;
+    row0 = p0 + pl * 256;
     has1 = 2 * pl + 1 < tiles;
     n0 = nt * BN;
   };
@@ -135,21 +150,27 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long prof_empty = 0;
+      (void)prof_empty;
+      int e_next = expert_of(cluster_id);
       for (int id = cluster_id; id < total && ok; id += n_clusters) {
         int e, row0, n0;
         bool has1;
-        decode(id, e, row0, has1, n0);
+        decode(id, e_next, e, row0, has1, n0);
+        e_next = expert_of(id + n_clusters);
         const bool load_a = leader || has1;
         const uint32_t bytes = (load_a ? kU2ABytes : 0) + kU2BBytes;
         const int my_row0 = row0 + (int)rank * 128;
         const int my_n0 = n0 + (int)rank * 128;
         for (int kb = 0; kb < kblocks; ++kb) {
+          YB_PROF_T0
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
             abort_flag = 1;
             atomicMax(p.header + kHdrStatus, (int)kStatusProducerTimeout);
             ok = false;
             break;
           }
+          YB_PROF_ADD(prof_empty)
           const uint32_t full = mapa_u32(smem_u32(&bar_full[stage]), 0);
           const uint32_t sa = smem_base + stage * kU2StageBytes;
           const uint32_t sb = sa + kU2ABytes;
@@ -164,6 +185,7 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (++stage == kU2Stages) { stage = 0; phase ^= 1u; }
         }
       }
+      YB_PROF_FLUSH(leader ? 0 : 1, prof_empty)
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -177,12 +199,25 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      long long prof_full = 0, prof_tmem = 0, prof_all = 0;
+      (void)prof_full; (void)prof_tmem; (void)prof_all;
+#ifdef YB_PROF
+      const long long prof_begin = clock64();
+#endif
       for (int id = cluster_id; id < total && ok; id += n_clusters) {
-        if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) { ok = false; break; }
+        {
+          YB_PROF_T0
+          if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) { ok = false; break; }
+          YB_PROF_ADD(prof_tmem)
+        }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kUmmaAccStride;
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) { ok = false; break; }
+          {
+            YB_PROF_T0
+            if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag)) { ok = false; break; }
+            YB_PROF_ADD(prof_full)
+          }
           tc_fence_after();
           const uint32_t sa = smem_base + stage * kU2StageBytes;
           const uint32_t sb = sa + kU2ABytes;
@@ -207,6 +242,12 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         abort_flag = 1;
         atomicMax(p.header + kHdrStatus, (int)kStatusMmaTimeout);
       }
+#ifdef YB_PROF
+      prof_all = clock64() - prof_begin;
+#endif
+      YB_PROF_FLUSH(2, prof_full)
+      YB_PROF_FLUSH(3, prof_tmem)
+      YB_PROF_FLUSH(4, prof_all)
     }
     __syncwarp();
   } else {
@@ -214,10 +255,12 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int e_next = expert_of(cluster_id);
     for (int id = cluster_id; id < total; id += n_clusters) {
       int e, row0, n0;
       bool has1;
-      decode(id, e, row0, has1, n0);
+      decode(id, e_next, e, row0, has1, n0);
+      e_next = expert_of(id + n_clusters);
       const int row = row0 + (int)rank * 128 + q * 32 + lane;
       if (!mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag)) {
         abort_flag = 1;

@@ -20,6 +20,7 @@
 #include "umma_gemm_swap.cuh"
 #include "gemv.cuh"
 #include "ep_p2p.cuh"
+#include "ep_fused.cuh"
 #include "router.cuh"
 
 namespace yb {
@@ -594,6 +595,146 @@ static int ep_local_backward_impl(const void* recv_x, const void* recv_g, const 
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
+
+// ---- expert parallelism as one chain of kernels (flags in symmetric memory) ----------------------
+// Workspace of a whole expert-parallel call: the plan / activation region of plan_ep first (so the
+// status word sits at the start of the workspace), then the tables of the local sort.
+struct EpCallPlan {
+  EpPlan ep;
+  RouteTables rt;          // local sort of this rank's assignments (no row tables)
+  size_t bytes = 0;
+};
+
+static EpCallPlan plan_ep_call(void* ws, const yamoe_ep_ctx_t& c, int64_t T, bool backward) {
+  EpCallPlan p;
+  p.ep = plan_ep(ws, c.max_rows, c.H, c.E, c.G, c.dtype, backward);
+  Bump b(ws);
+  b.off = p.ep.bytes;
+  const int64_t S = T * c.K;
+  p.rt.header = b.take<int32_t>(16);
+  p.rt.counts = b.take<int32_t>(c.E);
+  p.rt.bins = b.take<int32_t>(c.E + 1);
+  p.rt.pad_off = b.take<int32_t>(c.E + 1);
+  p.rt.block_counts = b.take<int32_t>((size_t)route_blocks(S > 0 ? S : 1) * c.E);
+  p.rt.sorted_values = b.take<int32_t>(S > 0 ? S : 1);
+  p.rt.sorted_indices = b.take<int32_t>(S > 0 ? S : 1);
+  p.rt.flat_pos = b.take<int32_t>(S > 0 ? S : 1);
+  p.bytes = b.off + 256;
+  return p;
+}
+
+static int check_ep_ctx(const yamoe_ep_ctx_t* c, bool backward) {
+  if (!c) return YAMOE_ERR_BAD_ARG;
+  int rc = check_ep(c->max_rows, c->H, c->E, c->G, c->rank, c->dtype);
+  if (rc) return rc;
+  if (c->K <= 0 || c->back_rows <= 0) return YAMOE_ERR_BAD_ARG;
+  if (!c->peer_recv_x || !c->peer_back || !c->peer_ctrl || !c->recv_x || !c->back || !c->ctrl || !c->state)
+    return YAMOE_ERR_BAD_ARG;
+  if (backward && (!c->peer_recv_g || !c->peer_recv_w || !c->peer_back_w || !c->recv_g || !c->recv_w || !c->back_w))
+    return YAMOE_ERR_BAD_ARG;
+  return YAMOE_OK;
+}
+
+// Steps shared by the forward and the backward call, up to the point where every row this rank's
+// experts need has arrived: local sort, count exchange, dispatch, row tables, wait.
+template <typename T>
+static int ep_call_prologue(const yamoe_ep_ctx_t& c, const EpCallPlan& p, const void* hidden, const void* grad,
+                            const int64_t* ridx, const void* rw, int rcols, int64_t Tn, int64_t cap,
+                            void* const* peer_back, cudaStream_t st) {
+  const int64_t S = Tn * c.K;
+  const uint64_t wait_ns = c.wait_ns ? c.wait_ns : kWaitLimitNs;
+  const EpCtrlLayout lay{c.G, c.E};
+  YB_CUDA_OK(cudaMemsetAsync(p.ep.t.rt.header, 0, 16 * sizeof(int32_t), st));
+  YB_CUDA_OK(cudaMemsetAsync(p.rt.header, 0, 16 * sizeof(int32_t), st));
+  if (S > 0) {
+    YB_CUDA_OK(cudaMemsetAsync(p.rt.flat_pos, 0xFF, (size_t)S * sizeof(int32_t), st));
+    int rc = launch_route<float>(ridx, nullptr, c.E, S, c.E, 1, (int64_t)1 << 40, p.rt, st);
+    if (rc) return rc;
+  } else {
+    YB_CUDA_OK(cudaMemsetAsync(p.rt.counts, 0, (size_t)c.E * sizeof(int32_t), st));
+    YB_CUDA_OK(cudaMemsetAsync(p.rt.bins, 0, (size_t)(c.E + 1) * sizeof(int32_t), st));
+  }
+  ep_publish_kernel<<<1, 256, 0, st>>>(p.rt.counts, reinterpret_cast<int32_t*>(c.state), c.peer_ctrl, lay, c.rank);
+  EpDispatchArgs a{};
+  a.hidden = hidden;
+  a.grad = grad;
+  a.routing_weights = grad ? rw : nullptr;
+  a.routing_cols = rcols;
+  a.sorted_values = p.rt.sorted_values;
+  a.sorted_indices = p.rt.sorted_indices;
+  a.bins = p.rt.bins;
+  a.peer_x = c.peer_recv_x;
+  a.peer_g = c.peer_recv_g;
+  a.peer_w = c.peer_recv_w;
+  a.peer_ctrl = c.peer_ctrl;
+  a.ctrl = reinterpret_cast<const int32_t*>(c.ctrl);
+  a.state = reinterpret_cast<int32_t*>(c.state);
+  a.max_rows = c.max_rows;
+  a.S = (int)S; a.H = c.H; a.E = c.E; a.G = c.G; a.rank = c.rank; a.K = c.K;
+  a.wait_ns = wait_ns;
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div(S, kRowWarps), (int64_t)umma_sm_count() * 6));
+  ep_dispatch_fused_kernel<T><<<grid, kRowWarps * 32, (size_t)(3 * c.E + 2) * sizeof(int32_t), st>>>(a, p.ep.t);
+  ep_rowtables_kernel<<<(unsigned)ceil_div(c.max_rows, 256), 256, 0, st>>>(
+      p.ep.t, cap, c.max_rows, peer_back, c.G, c.E / c.G, (int64_t)c.H * sizeof(T));
+  ep_wait_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const int32_t*>(c.ctrl) + lay.flag_dispatch(), c.G,
+                                   reinterpret_cast<const int32_t*>(c.state), p.ep.t.rt.header,
+                                   (int)kStatusEpDispatchTimeout, wait_ns);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+template <typename T>
+static int ep_forward_impl(const yamoe_ep_ctx_t& c, const void* hidden, const int64_t* ridx, const void* rw,
+                           int rcols, const void* wgu, const void* bgu, const void* wd, const void* bd, void* out,
+                           int64_t Tn, int64_t cap, void* ws, cudaStream_t st) {
+  const EpCallPlan p = plan_ep_call(ws, c, Tn, false);
+  const EpCtrlLayout lay{c.G, c.E};
+  const uint64_t wait_ns = c.wait_ns ? c.wait_ns : kWaitLimitNs;
+  int rc = ep_call_prologue<T>(c, p, hidden, nullptr, ridx, rw, rcols, Tn, cap, c.peer_back, st);
+  if (rc) return rc;
+  // gate_up + GLU + down on the received rows; the down GEMM's epilogue stores every result row
+  // into the back buffer of the rank that owns the token
+  rc = ep_local_forward_impl<T>(c.recv_x, wgu, bgu, wd, bd, nullptr, c.max_rows, c.H, c.E / c.G, c.dtype, p.ep, st);
+  if (rc) return rc;
+  ep_signal_kernel<<<1, 32, 0, st>>>(c.peer_ctrl, lay.flag_return(), c.G, c.rank,
+                                     reinterpret_cast<const int32_t*>(c.state));
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div(Tn, kRowWarps), (int64_t)umma_sm_count() * 8));
+  ep_combine_kernel<T, false><<<grid, kRowWarps * 32, 0, st>>>(
+      reinterpret_cast<const T*>(c.back), p.rt.flat_pos, ridx, reinterpret_cast<const T*>(rw), rcols,
+      reinterpret_cast<T*>(out), Tn, c.H, c.E, c.K, reinterpret_cast<const int32_t*>(c.ctrl) + lay.flag_return(), c.G,
+      reinterpret_cast<const int32_t*>(c.state), p.ep.t.rt.header, wait_ns);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+template <typename T>
+static int ep_backward_impl(const yamoe_ep_ctx_t& c, const void* grad_out, const void* hidden, const int64_t* ridx,
+                            const void* rw, int rcols, const void* wgu, const void* bgu, const void* wd,
+                            const void* bd, void* d_hidden, void* d_routing, void* d_wgu, void* d_bgu, void* d_wd,
+                            void* d_bd, int64_t Tn, int64_t cap, void* ws, cudaStream_t st) {
+  const EpCallPlan p = plan_ep_call(ws, c, Tn, true);
+  const EpCtrlLayout lay{c.G, c.E};
+  const uint64_t wait_ns = c.wait_ns ? c.wait_ns : kWaitLimitNs;
+  const int64_t S = Tn * c.K;
+  int rc = ep_call_prologue<T>(c, p, hidden, grad_out, ridx, rw, rcols, Tn, cap, c.peer_back, st);
+  if (rc) return rc;
+  rc = ep_local_backward_impl<T>(c.recv_x, c.recv_g, reinterpret_cast<const float*>(c.recv_w), wgu, bgu, wd, bd,
+                                 d_wgu, d_bgu, d_wd, d_bd, c.peer_back_w, cap, c.max_rows, c.H, c.E / c.G, c.G,
+                                 c.dtype, p.ep, st);
+  if (rc) return rc;
+  ep_signal_kernel<<<1, 32, 0, st>>>(c.peer_ctrl, lay.flag_return(), c.G, c.rank,
+                                     reinterpret_cast<const int32_t*>(c.state));
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div(Tn, kRowWarps), (int64_t)umma_sm_count() * 8));
+  ep_combine_kernel<T, true><<<grid, kRowWarps * 32, 0, st>>>(
+      reinterpret_cast<const T*>(c.back), p.rt.flat_pos, ridx, nullptr, rcols, reinterpret_cast<T*>(d_hidden), Tn,
+      c.H, c.E, c.K, reinterpret_cast<const int32_t*>(c.ctrl) + lay.flag_return(), c.G,
+      reinterpret_cast<const int32_t*>(c.state), p.ep.t.rt.header, wait_ns);
+  if (rcols == c.E) YB_CUDA_OK(cudaMemsetAsync(d_routing, 0, (size_t)Tn * rcols * sizeof(T), st));
+  if (S > 0)
+    ep_routing_grad_kernel<T><<<(unsigned)ceil_div(S, 256), 256, 0, st>>>(
+        reinterpret_cast<const float*>(c.back_w), p.rt.flat_pos, ridx, reinterpret_cast<T*>(d_routing), S, rcols, c.E,
+        c.K);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
 // ---- routing without a caller workspace -------------------------------------------------
 // Scratch for yamoe_b200_route_static.  It is part of the library image: every GPU that loads the
 // library keeps these bytes reserved until the process exits.  All calls on one device share it.
@@ -700,6 +841,9 @@ int yamoe_b200_route(const int64_t* router_indices, int32_t* sorted_values, int3
     if (counts) YB_CUDA_OK(cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int32_t), st));
     return YAMOE_OK;
   }
+  // ids outside [0, E) are dropped: the entries behind the last kept one read -1
+  YB_CUDA_OK(cudaMemsetAsync(sorted_values, 0xFF, (size_t)T * K * sizeof(int32_t), st));
+  YB_CUDA_OK(cudaMemsetAsync(sorted_indices, 0xFF, (size_t)T * K * sizeof(int32_t), st));
   return launch_route<float>(router_indices, nullptr, E, T, E, K, (int64_t)1 << 40, p.rt, st);
 }
 
@@ -735,6 +879,8 @@ int yamoe_b200_route_static(const int64_t* router_indices, int32_t* sorted_value
     if (counts) YB_CUDA_OK(cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int32_t), st));
     return YAMOE_OK;
   }
+  YB_CUDA_OK(cudaMemsetAsync(sorted_values, 0xFF, (size_t)T * K * sizeof(int32_t), st));
+  YB_CUDA_OK(cudaMemsetAsync(sorted_indices, 0xFF, (size_t)T * K * sizeof(int32_t), st));
   return launch_route<float>(router_indices, nullptr, E, T, E, K, (int64_t)1 << 40, rt, st);
 }
 
@@ -826,20 +972,21 @@ int yamoe_b200_batch_mm(const void* x, const void* weights, void* out, int E, in
   return batch_mm_impl<float>(x, weights, out, E, C, M, N, K, mode, workspace, st);
 }
 
-int yamoe_b200_permute_rows(const void* src, const int32_t* sorted_indices, void* dst, int64_t S, int H, int K,
-                            int dtype, void* stream) {
+int yamoe_b200_permute_rows(const void* src, int64_t n_src, const int32_t* sorted_indices, void* dst, int64_t S, int H,
+                            int K, int dtype, void* stream) {
   if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
-  if (S < 0 || H <= 0 || H % 8 != 0 || K <= 0) return YAMOE_ERR_BAD_ARG;
+  if (S < 0 || H <= 0 || H % 8 != 0 || K <= 0 || n_src < 0) return YAMOE_ERR_BAD_ARG;
   if (S == 0) return YAMOE_OK;
   if (!src || !sorted_indices || !dst) return YAMOE_ERR_BAD_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const unsigned blocks = (unsigned)ceil_div(S, kRowWarps);
   if (dtype == YAMOE_BF16)
     permute_rows_kernel<__nv_bfloat16><<<blocks, kRowWarps * 32, 0, st>>>(
-        reinterpret_cast<const __nv_bfloat16*>(src), sorted_indices, reinterpret_cast<__nv_bfloat16*>(dst), S, H, K);
+        reinterpret_cast<const __nv_bfloat16*>(src), sorted_indices, reinterpret_cast<__nv_bfloat16*>(dst), S, H, K,
+        n_src);
   else
-    permute_rows_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(reinterpret_cast<const float*>(src),
-                                                                 sorted_indices, reinterpret_cast<float*>(dst), S, H, K);
+    permute_rows_kernel<float><<<blocks, kRowWarps * 32, 0, st>>>(
+        reinterpret_cast<const float*>(src), sorted_indices, reinterpret_cast<float*>(dst), S, H, K, n_src);
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
@@ -858,7 +1005,7 @@ int yamoe_b200_combine_rows(const void* rows, const int32_t* sorted_indices, int
   int32_t* inv = reinterpret_cast<int32_t*>(workspace);
   YB_CUDA_OK(cudaMemsetAsync(inv, 0xFF, (size_t)T * K * sizeof(int32_t), st));
   if (n_sorted > 0)
-    invert_perm_kernel<<<(unsigned)ceil_div(n_sorted, 256), 256, 0, st>>>(sorted_indices, inv, n_sorted);
+    invert_perm_kernel<<<(unsigned)ceil_div(n_sorted, 256), 256, 0, st>>>(sorted_indices, inv, n_sorted, T * K);
   const unsigned blocks = (unsigned)ceil_div(T, kRowWarps);
   if (dtype == YAMOE_BF16)
     combine_rows_kernel<__nv_bfloat16><<<blocks, kRowWarps * 32, 0, st>>>(
@@ -1007,6 +1154,79 @@ int yamoe_b200_ep_local_backward(const void* recv_x, const void* recv_g, const f
                                        p, st);
 }
 
+size_t yamoe_b200_ep_ctrl_bytes(int G, int E) {
+  if (G <= 0 || E <= 0) return 0;
+  return (size_t)EpCtrlLayout{G, E}.words() * sizeof(int32_t);
+}
+
+size_t yamoe_b200_ep_call_workspace_bytes(const yamoe_ep_ctx_t* ctx, int64_t T, int backward) {
+  if (check_ep_ctx(ctx, false) || T < 0) return 0;
+  return plan_ep_call(nullptr, *ctx, T, backward != 0).bytes;
+}
+
+int yamoe_b200_ep_forward(const yamoe_ep_ctx_t* ctx, const void* hidden_states, const int64_t* router_indices,
+                          const void* routing_weights, int routing_cols, const void* gate_up_proj,
+                          const void* gate_up_proj_bias, const void* down_proj, const void* down_proj_bias,
+                          void* out, int64_t T, int64_t expert_capacity, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  int rc = check_ep_ctx(ctx, false);
+  if (rc) return rc;
+  if (T < 0 || expert_capacity < 0 || T * ctx->K > ctx->back_rows) return YAMOE_ERR_BAD_ARG;
+  if (routing_cols != ctx->E && routing_cols != ctx->K) return YAMOE_ERR_BAD_ARG;
+  if (T > 0 && (!hidden_states || !router_indices || !routing_weights || !out)) return YAMOE_ERR_BAD_ARG;
+  if (!gate_up_proj || !gate_up_proj_bias || !down_proj || !down_proj_bias) return YAMOE_ERR_BAD_ARG;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < yamoe_b200_ep_call_workspace_bytes(ctx, T, 0))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (ctx->dtype == YAMOE_BF16)
+    return ep_forward_impl<__nv_bfloat16>(*ctx, hidden_states, router_indices, routing_weights, routing_cols,
+                                          gate_up_proj, gate_up_proj_bias, down_proj, down_proj_bias, out, T,
+                                          expert_capacity, workspace, st);
+  return ep_forward_impl<float>(*ctx, hidden_states, router_indices, routing_weights, routing_cols, gate_up_proj,
+                                gate_up_proj_bias, down_proj, down_proj_bias, out, T, expert_capacity, workspace, st);
+}
+
+int yamoe_b200_ep_backward(const yamoe_ep_ctx_t* ctx, const void* grad_out, const void* hidden_states,
+                           const int64_t* router_indices, const void* routing_weights, int routing_cols,
+                           const void* gate_up_proj, const void* gate_up_proj_bias, const void* down_proj,
+                           const void* down_proj_bias, void* d_hidden, void* d_routing, void* d_gate_up_proj,
+                           void* d_gate_up_proj_bias, void* d_down_proj, void* d_down_proj_bias, int64_t T,
+                           int64_t expert_capacity, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_ep_ctx(ctx, true);
+  if (rc) return rc;
+  if (T < 0 || expert_capacity < 0 || T * ctx->K > ctx->back_rows) return YAMOE_ERR_BAD_ARG;
+  if (routing_cols != ctx->E && routing_cols != ctx->K) return YAMOE_ERR_BAD_ARG;
+  if (T > 0 && (!grad_out || !hidden_states || !router_indices || !routing_weights || !d_hidden || !d_routing))
+    return YAMOE_ERR_BAD_ARG;
+  if (!gate_up_proj || !gate_up_proj_bias || !down_proj || !down_proj_bias || !d_gate_up_proj ||
+      !d_gate_up_proj_bias || !d_down_proj || !d_down_proj_bias)
+    return YAMOE_ERR_BAD_ARG;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      workspace_bytes < yamoe_b200_ep_call_workspace_bytes(ctx, T, 1))
+    return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (ctx->dtype == YAMOE_BF16)
+    return ep_backward_impl<__nv_bfloat16>(*ctx, grad_out, hidden_states, router_indices, routing_weights,
+                                           routing_cols, gate_up_proj, gate_up_proj_bias, down_proj, down_proj_bias,
+                                           d_hidden, d_routing, d_gate_up_proj, d_gate_up_proj_bias, d_down_proj,
+                                           d_down_proj_bias, T, expert_capacity, workspace, st);
+  return ep_backward_impl<float>(*ctx, grad_out, hidden_states, router_indices, routing_weights, routing_cols,
+                                 gate_up_proj, gate_up_proj_bias, down_proj, down_proj_bias, d_hidden, d_routing,
+                                 d_gate_up_proj, d_gate_up_proj_bias, d_down_proj, d_down_proj_bias, T,
+                                 expert_capacity, workspace, st);
+}
+
+int yamoe_b200_ep_wait_probe(const int32_t* flags, int G, int32_t epoch, uint64_t wait_ns, int32_t* state,
+                             int32_t* header, void* stream) {
+  if (!flags || !state || !header || G <= 0 || G > 256) return YAMOE_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  YB_CUDA_OK(cudaMemcpyAsync(state + kEpStateEpoch, &epoch, sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  YB_CUDA_OK(cudaMemsetAsync(header, 0, 16 * sizeof(int32_t), st));
+  ep_wait_kernel<<<1, 32, 0, st>>>(flags, G, state, header, (int)kStatusEpDispatchTimeout, wait_ns ? wait_ns : 1000000ull);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
 int yamoe_b200_router_topk(const void* router_logits, int64_t* router_indices, void* router_scores, int64_t T, int E,
                            int K, int dtype, void* stream) {
   if (dtype != YAMOE_F32 && dtype != YAMOE_BF16) return YAMOE_ERR_DTYPE;
@@ -1128,6 +1348,24 @@ int yamoe_b200_index_select(void* out, const void* in, const int32_t* idx, int64
   else
     index_select_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(in), idx,
                                                        reinterpret_cast<float*>(out), N);
+  return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+#ifdef YB_PROF
+int yamoe_b200_prof_read(unsigned long long* out16) {
+  unsigned long long zero[16] = {};
+  if (cudaDeviceSynchronize() != cudaSuccess) return YAMOE_ERR_CUDA;
+  if (cudaMemcpyFromSymbol(out16, g_prof, sizeof(zero)) != cudaSuccess) return YAMOE_ERR_CUDA;
+  if (cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)) != cudaSuccess) return YAMOE_ERR_CUDA;
+  return YAMOE_OK;
+}
+#endif
+
+int yamoe_b200_mbar_wait_probe(void* workspace, uint64_t limit_ns, void* stream) {
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255)) return YAMOE_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  YB_CUDA_OK(cudaMemsetAsync(workspace, 0, 16 * sizeof(int32_t), st));
+  mbar_wait_probe_kernel<<<1, 32, 0, st>>>(reinterpret_cast<int32_t*>(workspace), limit_ns ? limit_ns : 1000000ull);
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 

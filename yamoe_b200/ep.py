@@ -175,151 +175,136 @@ def ep_experts_backward(grad_out, hidden_states, router_indices, routing_weights
 
 class PeerExpertParallel:
     """Expert-parallel forward (and, with `backward=True`, backward) whose dispatch and combine are
-    peer stores over NVLink.
+    peer stores over NVLink and whose phase boundaries are flags in symmetric memory.
 
-    All offsets come from the all-gathered [G, E] count matrix on the device: a call makes no
-    device-to-host copy and needs no split sizes.  Buffers that peers write into are symmetric
-    allocations made once, sized for `max_tokens_total` tokens over all ranks (worst case: every
-    assignment lands on one rank) and `max_tokens_local` tokens on this rank.
+    One call is ONE entry into the library (`yamoe_b200_ep_forward` / `yamoe_b200_ep_backward`): a
+    fixed chain of kernels on the current stream, with no NCCL collective, no device-to-host copy
+    and no split sizes.  Per call: local sort -> my per-expert counts to every rank (flag) ->
+    dispatch kernel (waits for all counts, derives every offset on the device, stores my rows into
+    the owners' GEMM input layout, flag) -> wait for all sources -> grouped GEMMs on the received
+    rows, the last one storing each result row straight into the token owner's buffer from its
+    epilogue (flag) -> combine kernel (waits for all owners).  Every wait is bounded
+    (`wait_seconds`); `status()` reads the device status word of the last call.
 
-    Sequence per call (one stream): route -> all_gather(counts) -> plan -> dispatch (peer stores) ->
-    barrier -> grouped GEMMs on the received rows, the down GEMM's epilogue storing each result row
-    straight into the token owner's buffer (`fused_return`; otherwise a separate return kernel) ->
-    barrier -> combine.
-    The barriers are stream-ordered collectives; no kernel of this path waits on another GPU.
+    Buffers that peers write into are symmetric allocations made once, sized for
+    `max_tokens_total` tokens over all ranks (worst case: every assignment lands on one rank) and
+    `max_tokens_local` tokens on this rank.  Construction is collective (it ends with a barrier);
+    afterwards all ranks must make the same sequence of forward / backward calls.
     """
 
     def __init__(self, hidden: int, num_experts: int, top_k: int, max_tokens_total: int, max_tokens_local: int,
-                 dtype=torch.bfloat16, group=None, fused_return: bool = False, backward: bool = False):
+                 dtype=torch.bfloat16, group=None, backward: bool = False, wait_seconds: float = 2.0):
+        import ctypes
         import torch.distributed._symmetric_memory as symm_mem
-        self.fused_return = bool(fused_return)
         from . import _lib
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.H, self.E, self.K, self.dtype = int(hidden), int(num_experts), int(top_k), dtype
         if self.E % self.world:
             raise ValueError("num_experts must be divisible by the group size")
+        if max_tokens_local > max_tokens_total:
+            raise ValueError("max_tokens_local cannot exceed max_tokens_total")
         self.per = self.E // self.world
         self.dt = _lib.YAMOE_BF16 if dtype == torch.bfloat16 else _lib.YAMOE_F32
-        s_total = max_tokens_total * self.K
+        s_total = int(max_tokens_total) * self.K
         self.max_rows = ((s_total + 127) // 128 + self.per) * 128
-        self.s_local = max_tokens_local * self.K
+        self.s_local = max(int(max_tokens_local) * self.K, 1)
+        self.t_local = int(max_tokens_local)
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.recv = symm_mem.empty(self.max_rows, self.H, dtype=dtype, device=dev)
-        self.back = symm_mem.empty(max(self.s_local, 1), self.H, dtype=dtype, device=dev)
-        h_recv = symm_mem.rendezvous(self.recv, self.group)
-        h_back = symm_mem.rendezvous(self.back, self.group)
-        self.peer_recv = torch.tensor(list(h_recv.buffer_ptrs), dtype=torch.int64, device=dev)
-        self.peer_back = torch.tensor(list(h_back.buffer_ptrs), dtype=torch.int64, device=dev)
-        self._handles = [h_recv, h_back]
-        self.L = _lib.lib()
+        self.L = L = _lib.lib()
+        self._check = _lib.check
         self.has_backward = bool(backward)
+
+        def symmetric(shape, dt):
+            t = symm_mem.empty(*shape, dtype=dt, device=dev)
+            t.zero_()
+            h = symm_mem.rendezvous(t, self.group)
+            ptrs = torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=dev)
+            self._keep.append((t, h, ptrs))
+            return t, ptrs
+
+        self._keep = []
+        # padding rows of the receive buffers enter the weight-gradient GEMMs as the k dimension
+        # (times zero): they must hold finite values, hence the zero fill
+        self.recv, p_recv = symmetric((self.max_rows, self.H), dtype)
+        self.back, p_back = symmetric((self.s_local, self.H), dtype)
+        ctrl_words = L.yamoe_b200_ep_ctrl_bytes(self.world, self.E) // 4
+        self.ctrl, p_ctrl = symmetric((ctrl_words,), torch.int32)
+        ctx = _lib.EpCtx(G=self.world, rank=self.rank, E=self.E, K=self.K, H=self.H, dtype=self.dt,
+                         max_rows=self.max_rows, back_rows=self.s_local,
+                         peer_recv_x=p_recv.data_ptr(), peer_back=p_back.data_ptr(), peer_ctrl=p_ctrl.data_ptr(),
+                         recv_x=self.recv.data_ptr(), back=self.back.data_ptr(), ctrl=self.ctrl.data_ptr(),
+                         wait_ns=int(wait_seconds * 1e9))
         if self.has_backward:
             # upstream-gradient rows and routing weights travel to the expert owners, routing-weight
             # gradients travel back: three more buffers that peers write into
-            self.recv_g = symm_mem.empty(self.max_rows, self.H, dtype=dtype, device=dev)
-            self.recv_w = symm_mem.empty(self.max_rows, dtype=torch.float32, device=dev)
-            self.back_w = symm_mem.empty(max(self.s_local, 1), dtype=torch.float32, device=dev)
-            hs_ = [symm_mem.rendezvous(t, self.group) for t in (self.recv_g, self.recv_w, self.back_w)]
-            self.peer_recv_g, self.peer_recv_w, self.peer_back_w = (
-                torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=dev) for h in hs_)
-            self._handles += hs_
-        ws_bytes = self.L.yamoe_b200_ep_backward_workspace_bytes if self.has_backward \
-            else self.L.yamoe_b200_ep_workspace_bytes
-        nbytes = ws_bytes(self.max_rows, self.H, self.E, self.world, self.dt)
+            self.recv_g, p_recv_g = symmetric((self.max_rows, self.H), dtype)
+            self.recv_w, p_recv_w = symmetric((self.max_rows,), torch.float32)
+            self.back_w, p_back_w = symmetric((self.s_local,), torch.float32)
+            ctx.peer_recv_g, ctx.peer_recv_w, ctx.peer_back_w = (p_recv_g.data_ptr(), p_recv_w.data_ptr(),
+                                                                   p_back_w.data_ptr())
+            ctx.recv_g, ctx.recv_w, ctx.back_w = self.recv_g.data_ptr(), self.recv_w.data_ptr(), self.back_w.data_ptr()
+        self.state = torch.zeros(64, dtype=torch.int32, device=dev)
+        ctx.state = self.state.data_ptr()
+        self.ctx = ctx
+        self._ctx_ref = ctypes.byref(ctx)
+        nbytes = L.yamoe_b200_ep_call_workspace_bytes(self._ctx_ref, self.t_local, int(self.has_backward))
         if nbytes == 0:
             raise RuntimeError("yamoe_b200: unsupported expert-parallel configuration")
         self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-        self.y_rows = torch.empty(self.max_rows, self.H, dtype=dtype, device=dev)
-        self.counts_all = torch.empty(self.world, self.E, dtype=torch.int32, device=dev)
-        self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
-        self._check = _lib.check
-        # padding rows of the receive buffer enter the weight-gradient GEMMs as the k dimension
-        # (times zero): they must hold finite values, so start from zeros before any peer writes
-        self.recv.zero_()
-        self._barrier()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)       # every rank's control block is zero before anyone publishes
 
-    def _barrier(self):
-        dist.all_reduce(self.flag, group=self.group)      # stream-ordered; orders the peer stores
+    def status(self) -> int:
+        """Device status word of the last call (synchronises the current stream): 0 = every wait
+        completed; 4 / 5 / 6 = the wait for counts / dispatched rows / returned rows gave up;
+        7 = the rows routed to one rank exceed the receive buffers; 1-3 = a GEMM pipeline wait."""
+        import ctypes
+        out = ctypes.c_int32(0)
+        self._check(self.L.yamoe_b200_device_status(self.ws.data_ptr(), torch.cuda.current_stream().cuda_stream,
+                                                    ctypes.byref(out)), "device_status")
+        return int(out.value)
+
+    def _common(self, hidden_states, router_indices, routing_weights):
+        T, K = router_indices.shape
+        if T > self.t_local or K != self.K or hidden_states.shape[1] != self.H:
+            raise RuntimeError("PeerExpertParallel: call exceeds the sizes the buffers were made for")
+        if hidden_states.dtype != self.dtype or routing_weights.dtype != self.dtype:
+            raise RuntimeError("PeerExpertParallel: dtype differs from the one the buffers were made for")
+        rw = routing_weights.contiguous()
+        if rw.shape[1] not in (self.K, self.E):
+            raise RuntimeError("routing_weights must be [T, K] or [T, E]")
+        return T, hidden_states.contiguous(), router_indices.to(torch.int64).contiguous(), rw
 
     def forward(self, hidden_states, router_indices, routing_weights, gate_up_local, gate_up_bias_local,
                 down_local, down_bias_local, expert_capacity: int):
-        from . import ops
-        T, K = router_indices.shape
-        if T * K > self.s_local or K != self.K or hidden_states.shape[1] != self.H:
-            raise RuntimeError("PeerExpertParallel: call exceeds the sizes the buffers were made for")
-        L, st = self.L, torch.cuda.current_stream().cuda_stream
-        hs = hidden_states.contiguous()
-        sv, si, bins, counts = ops.route(router_indices, self.E)
-        dist.all_gather_into_tensor(self.counts_all.view(-1), counts, group=self.group)
-        self._check(L.yamoe_b200_ep_plan(self.counts_all.data_ptr(), self.world, self.rank, self.E,
-                                         int(expert_capacity), self.peer_back.data_ptr(), self.max_rows, self.H,
-                                         self.dt, self.ws.data_ptr(), self.ws.numel(), st), "ep_plan")
-        self._check(L.yamoe_b200_ep_dispatch(hs.data_ptr(), sv.data_ptr(), si.data_ptr(), bins.data_ptr(), T * K,
-                                             self.peer_recv.data_ptr(), self.max_rows, self.H, self.E, self.world, K,
-                                             self.dt, self.ws.data_ptr(), st), "ep_dispatch")
-        self._barrier()
-        y_ptr = None if self.fused_return else self.y_rows.data_ptr()
-        self._check(L.yamoe_b200_ep_local_forward(self.recv.data_ptr(), gate_up_local.data_ptr(),
-                                                  gate_up_bias_local.data_ptr(), down_local.data_ptr(),
-                                                  down_bias_local.data_ptr(), y_ptr, self.max_rows,
-                                                  self.H, self.E, self.world, self.dt, self.ws.data_ptr(), st),
-                    "ep_local_forward")
-        if not self.fused_return:
-            self._check(L.yamoe_b200_ep_return(self.y_rows.data_ptr(), self.peer_back.data_ptr(), self.max_rows,
-                                               self.H, self.E, self.world, self.dt, self.ws.data_ptr(), st),
-                        "ep_return")
-        self._barrier()
-        return ops.combine_rows(self.back[: T * K], si, router_indices, routing_weights, self.E)
+        T, hs, ri, rw = self._common(hidden_states, router_indices, routing_weights)
+        if gate_up_local.shape[0] != self.per:
+            raise RuntimeError(f"expected {self.per} local experts, got {gate_up_local.shape[0]}")
+        out = torch.empty_like(hs)
+        st = torch.cuda.current_stream().cuda_stream
+        self._check(self.L.yamoe_b200_ep_forward(
+            self._ctx_ref, hs.data_ptr(), ri.data_ptr(), rw.data_ptr(), rw.shape[1], gate_up_local.data_ptr(),
+            gate_up_bias_local.data_ptr(), down_local.data_ptr(), down_bias_local.data_ptr(), out.data_ptr(), T,
+            int(expert_capacity), self.ws.data_ptr(), self.ws.numel(), st), "ep_forward")
+        return out
 
     def backward(self, grad_out, hidden_states, router_indices, routing_weights, gate_up_local, gate_up_bias_local,
                  down_local, down_bias_local, expert_capacity: int):
         """Expert-parallel `experts_backward` over the same peer buffers (made with `backward=True`).
         Returns what `ep_experts_backward` returns: (d_hidden [T_r,H], d_routing [T_r, cols],
         d_gate_up_local, d_gate_up_bias_local, d_down_local, d_down_bias_local)."""
-        from . import ops
         if not self.has_backward:
             raise RuntimeError("PeerExpertParallel: made without backward=True")
-        T, K = router_indices.shape
-        H, E = self.H, self.E
-        if T * K > self.s_local or K != self.K or hidden_states.shape[1] != H:
-            raise RuntimeError("PeerExpertParallel: call exceeds the sizes the buffers were made for")
-        L, st = self.L, torch.cuda.current_stream().cuda_stream
-        dt, dev = hidden_states.dtype, hidden_states.device
-        hs = hidden_states.contiguous()
-        go = grad_out.reshape(T, H).contiguous()
-        rw = routing_weights.contiguous()
-        rcols = rw.shape[1]
-        sv, si, bins, counts = ops.route(router_indices, E)
-        dist.all_gather_into_tensor(self.counts_all.view(-1), counts, group=self.group)
-        ws, S = self.ws.data_ptr(), T * K
-        self._check(L.yamoe_b200_ep_plan(self.counts_all.data_ptr(), self.world, self.rank, E, int(expert_capacity),
-                                         self.peer_back.data_ptr(), self.max_rows, H, self.dt, ws, self.ws.numel(),
-                                         st), "ep_plan")
-        for src, peers in ((hs, self.peer_recv), (go, self.peer_recv_g)):
-            self._check(L.yamoe_b200_ep_dispatch(src.data_ptr(), sv.data_ptr(), si.data_ptr(), bins.data_ptr(), S,
-                                                 peers.data_ptr(), self.max_rows, H, E, self.world, K, self.dt, ws,
-                                                 st), "ep_dispatch")
-        self._check(L.yamoe_b200_ep_dispatch_weights(rw.data_ptr(), rcols, sv.data_ptr(), si.data_ptr(),
-                                                     bins.data_ptr(), S, self.peer_recv_w.data_ptr(), self.max_rows,
-                                                     H, E, self.world, K, self.dt, ws, st), "ep_dispatch_weights")
-        self._barrier()
+        T, hs, ri, rw = self._common(hidden_states, router_indices, routing_weights)
+        go = grad_out.reshape(T, self.H).contiguous()
+        d_hidden, d_routing = torch.empty_like(hs), torch.empty_like(rw)
         d_wgu, d_bgu = torch.empty_like(gate_up_local), torch.empty_like(gate_up_bias_local)
         d_wd, d_bd = torch.empty_like(down_local), torch.empty_like(down_bias_local)
-        self._check(L.yamoe_b200_ep_local_backward(
-            self.recv.data_ptr(), self.recv_g.data_ptr(), self.recv_w.data_ptr(), gate_up_local.data_ptr(),
-            gate_up_bias_local.data_ptr(), down_local.data_ptr(), down_bias_local.data_ptr(), d_wgu.data_ptr(),
-            d_bgu.data_ptr(), d_wd.data_ptr(), d_bd.data_ptr(), self.peer_back_w.data_ptr(), int(expert_capacity),
-            self.max_rows, H, E, self.world, self.dt, ws, self.ws.numel(), st), "ep_local_backward")
-        self._barrier()
-        n_sorted = si.numel()
-        ones = torch.ones(T, K, dtype=dt, device=dev)
-        d_hidden = ops.combine_rows(self.back[:S], si, router_indices, ones, E)
-        d_sel = torch.zeros(S, dtype=dt, device=dev)
-        d_sel[si.long()] = self.back_w[:n_sorted].to(dt)
-        if rcols == E:
-            d_routing = torch.zeros(T, E, dtype=dt, device=dev)
-            d_routing.scatter_(1, router_indices.to(torch.int64), d_sel.view(T, K))
-        else:
-            d_routing = d_sel.view(T, K)
+        st = torch.cuda.current_stream().cuda_stream
+        self._check(self.L.yamoe_b200_ep_backward(
+            self._ctx_ref, go.data_ptr(), hs.data_ptr(), ri.data_ptr(), rw.data_ptr(), rw.shape[1],
+            gate_up_local.data_ptr(), gate_up_bias_local.data_ptr(), down_local.data_ptr(), down_bias_local.data_ptr(),
+            d_hidden.data_ptr(), d_routing.data_ptr(), d_wgu.data_ptr(), d_bgu.data_ptr(), d_wd.data_ptr(),
+            d_bd.data_ptr(), T, int(expert_capacity), self.ws.data_ptr(), self.ws.numel(), st), "ep_backward")
         return d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd

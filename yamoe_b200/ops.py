@@ -6,6 +6,8 @@ tensor with torch, pass raw pointers and torch's current stream.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -45,6 +47,14 @@ def _stream() -> int:
 
 def _workspace(nbytes: int, device) -> torch.Tensor:
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _check_device_status(ws: torch.Tensor, what: str) -> None:
+    """With YAMOE_B200_CHECK_STATUS=1 every expert call is followed by a read of the device status
+    word of its workspace (one stream synchronisation): a bounded wait inside a kernel that gave up
+    then raises instead of returning partly written outputs.  Off by default (no host sync)."""
+    if os.environ.get("YAMOE_B200_CHECK_STATUS", "0") not in ("", "0"):
+        _lib.check_device_status(ws.data_ptr(), _stream(), what)
 
 
 def _validate(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias, down_proj,
@@ -101,6 +111,7 @@ def _experts_cuda(hidden_states, router_indices, routing_weights, gate_up_proj, 
                                           bgu.data_ptr(), wd.data_ptr(), bd.data_ptr(), out.data_ptr(), T, H, E, K,
                                           int(expert_capacity), dt, ws.data_ptr(), ws.numel(), _stream())
         _lib.check(st, "experts")
+        _check_device_status(ws, "experts")
     return out
 
 
@@ -134,6 +145,7 @@ def _experts_backward_cuda(grad_out, hidden_states, router_indices, routing_weig
                                            d_bgu.data_ptr(), d_wd.data_ptr(), d_bd.data_ptr(), T, H, E, K,
                                            int(expert_capacity), dt, ws.data_ptr(), ws.numel(), _stream())
         _lib.check(st, "experts_backward")
+        _check_device_status(ws, "experts_backward")
     return [d_hidden, d_routing, d_wgu, d_bgu, d_wd, d_bd]
 
 
@@ -326,8 +338,8 @@ def permute_rows(src: torch.Tensor, sorted_indices: torch.Tensor, top_k: int) ->
     src, si = src.contiguous(), sorted_indices.contiguous()
     out = torch.empty(si.numel(), src.shape[1], dtype=src.dtype, device=src.device)
     with torch.cuda.device(src.device):
-        st = _lib.lib().yamoe_b200_permute_rows(src.data_ptr(), si.data_ptr(), out.data_ptr(), si.numel(),
-                                                src.shape[1], int(top_k), _DT[src.dtype], _stream())
+        st = _lib.lib().yamoe_b200_permute_rows(src.data_ptr(), src.shape[0], si.data_ptr(), out.data_ptr(),
+                                                si.numel(), src.shape[1], int(top_k), _DT[src.dtype], _stream())
         _lib.check(st, "permute_rows")
     return out
 
