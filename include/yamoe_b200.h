@@ -186,74 +186,13 @@ int yamoe_b200_combine_rows(const void *rows, const int32_t *sorted_indices, int
                             size_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
- * Expert parallelism over peer memory (no counterpart in the reference).  G ranks, rank r owns
- * experts [r*E/G, (r+1)*E/G).  `peer_recv` / `peer_back` are DEVICE arrays of G pointers to
- * buffers every rank allocated with the same size and made peer-accessible:
- *   recv  [max_rows, H]  rows this rank's experts receive, in the padded expert-sorted layout
- *   back  [S_max, H]     result rows of this rank's own assignments, in its sorted order
- * max_rows must be a multiple of 128 and at least (total assignments of all ranks) + 128*E/G.
- * One forward call is, on every rank and on one stream:
- *   yamoe_b200_route            local stable sort -> sorted_values, sorted_indices, bins, counts
- *   (all-gather of counts)      -> counts_all [G, E] on the device
- *   yamoe_b200_ep_plan          offsets, local tile tables and row validity, all on the device
- *   yamoe_b200_ep_dispatch      hidden rows -> owner's recv buffer (peer stores)
- *   (any stream-ordered collective as a barrier)
- *   yamoe_b200_ep_local_forward gate_up + GLU + down on the received rows.  With y_rows == NULL the
- *                               down GEMM's epilogue stores every result row straight into the
- *                               source rank's back buffer (GEMM and combine exchange in one
- *                               kernel; needs peer_back given to ep_plan); otherwise it writes
- *                               y_rows [max_rows, H] and
- *   yamoe_b200_ep_return        sends them (peer stores; zeros if dropped)
- *   (barrier)                   then yamoe_b200_combine_rows on `back`
- * No host synchronisation and no host-side split sizes are involved.  The kernels only store
- * to peer memory; none of them reads from or waits on another GPU.
- * ------------------------------------------------------------------------------------------- */
-size_t yamoe_b200_ep_workspace_bytes(int64_t max_rows, int H, int E, int G, int dtype);
-int yamoe_b200_ep_plan(const int32_t *counts_all, int G, int rank, int E, int64_t expert_capacity,
-                       void *const *peer_back, int64_t max_rows, int H, int dtype, void *workspace,
-                       size_t workspace_bytes, void *stream);
-int yamoe_b200_ep_dispatch(const void *hidden_states, const int32_t *sorted_values, const int32_t *sorted_indices,
-                           const int32_t *bins, int64_t S, void *const *peer_recv, int64_t max_rows, int H, int E,
-                           int G, int K, int dtype, const void *workspace, void *stream);
-int yamoe_b200_ep_local_forward(const void *recv_x, const void *gate_up_proj, const void *gate_up_proj_bias,
-                                const void *down_proj, const void *down_proj_bias, void *y_rows, int64_t max_rows,
-                                int H, int E, int G, int dtype, void *workspace, void *stream);
-int yamoe_b200_ep_return(const void *y_rows, void *const *peer_back, int64_t max_rows, int H, int E, int G,
-                         int dtype, const void *workspace, void *stream);
-
-/* Backward over the same peer buffers.  Three more symmetric buffers per rank: recv_g
- * [max_rows, H] (upstream-gradient rows), recv_w [max_rows] fp32 (routing weight of every row)
- * and back_w [S_local] fp32 (routing-weight gradients on their way home).  The workspace is the
- * forward one with more behind it (yamoe_b200_ep_backward_workspace_bytes), so plan and dispatch
- * take it unchanged.  One call is:
- *   route, all-gather of counts, yamoe_b200_ep_plan (peer_back = the d_hidden row buffers)
- *   yamoe_b200_ep_dispatch(hidden -> recv_x), yamoe_b200_ep_dispatch(grad_out -> recv_g),
- *   yamoe_b200_ep_dispatch_weights(routing_weights [T, routing_cols] -> recv_w)
- *   (barrier)
- *   yamoe_b200_ep_local_backward   recompute, the four gradient GEMMs and both bias gradients for
- *                                  the local experts; the input-gradient rows leave through the
- *                                  last data-gradient GEMM's epilogue into peer_back, the
- *                                  routing-weight gradients into peer_back_w
- *   (barrier)                      then yamoe_b200_combine_rows with unit weights on `back`
- *                                  (= d_hidden) and a scatter of back_w through sorted_indices.
- * Weight and bias gradients stay with the expert's owner: experts are not replicated. */
-size_t yamoe_b200_ep_backward_workspace_bytes(int64_t max_rows, int H, int E, int G, int dtype);
-int yamoe_b200_ep_dispatch_weights(const void *routing_weights, int routing_cols, const int32_t *sorted_values,
-                                   const int32_t *sorted_indices, const int32_t *bins, int64_t S,
-                                   void *const *peer_recv_w, int64_t max_rows, int H, int E, int G, int K, int dtype,
-                                   const void *workspace, void *stream);
-int yamoe_b200_ep_local_backward(const void *recv_x, const void *recv_g, const float *recv_w,
-                                 const void *gate_up_proj, const void *gate_up_proj_bias, const void *down_proj,
-                                 const void *down_proj_bias, void *d_gate_up_proj, void *d_gate_up_proj_bias,
-                                 void *d_down_proj, void *d_down_proj_bias, void *const *peer_back_w,
-                                 int64_t expert_capacity, int64_t max_rows, int H, int E, int G, int dtype,
-                                 void *workspace, size_t workspace_bytes, void *stream);
-
-/* ---------------------------------------------------------------------------------------------
  * Expert parallelism as ONE call per rank (no counterpart in the reference, which is single-GPU).
- * The count exchange and the phase boundaries of the peer-store path above are flags in
- * peer-writable memory instead of host-issued collectives: a call enqueues a fixed chain of
- * kernels on `stream` and nothing else -- no NCCL call, no host synchronisation, no split sizes.
+ * G ranks, rank r owns experts [r*E/G, (r+1)*E/G) and a shard of the tokens.  Token rows travel to
+ * the expert owners and result rows back as peer stores over NVLink; every offset is derived on
+ * the device from the per-rank expert counts, and the count exchange and the phase boundaries are
+ * flags in peer-writable memory instead of host-issued collectives: a call enqueues a fixed chain
+ * of kernels on `stream` and nothing else -- no NCCL call, no host synchronisation, no split
+ * sizes.  Kernels only STORE to peer memory; every wait polls local memory.
  *
  * Buffers (each allocated by every rank with the same size and made peer-accessible; the
  * peer_* members are DEVICE arrays of G pointers, index = rank, own buffer included):
@@ -335,6 +274,19 @@ int yamoe_b200_index_select(void *out, const void *in, const int32_t *idx, int64
  * ------------------------------------------------------------------------------------------- */
 int yamoe_b200_router_topk(const void *router_logits, int64_t *router_indices, void *router_scores, int64_t T,
                            int E, int K, int dtype, void *stream);
+
+/* Whole router of the layer in front of the expert op, replacing the chain
+ * F.linear -> topk -> softmax -> zeros_like().scatter_() of Yamoe.forward
+ * (torch-ext/yamoe/layers.py:126-149; oracle torch-ext/yamoe/vendored/gpt_oss_mlp.py:119-139):
+ *   logits = hidden_states [T,H] @ router_weight [E,H]^T + router_bias [E]   (rounded to `dtype`)
+ * followed by what yamoe_b200_router_topk does.  For bf16 with H a multiple of 64 and E <= 256 this is
+ * ONE kernel (a tcgen05 GEMM whose epilogue does the top-k, softmax and scatter); otherwise the
+ * CUDA-core GEMM and the top-k kernel run back to back.  router_bias may be NULL.  The workspace
+ * (256-byte aligned, yamoe_b200_router_workspace_bytes) holds the logits and a status header. */
+size_t yamoe_b200_router_workspace_bytes(int64_t T, int E);
+int yamoe_b200_router_forward(const void *hidden_states, const void *router_weight, const void *router_bias,
+                              int64_t *router_indices, void *router_scores, int64_t T, int H, int E, int K,
+                              int dtype, void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Training pair that keeps activations instead of recomputing them (the reference's autograd

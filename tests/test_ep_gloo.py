@@ -120,3 +120,53 @@ def test_expert_range_and_sharding():
     w = torch.arange(8 * 2 * 4).view(8, 2, 4).float()
     shard = ep.shard_expert_weights(w, w[:, 0], w[:, :, :2], w[:, 0, :2], 1, 4)
     assert shard[0].shape == (2, 2, 4) and torch.equal(shard[0], w[2:4])
+
+
+def _leaver_worker(rank, world, port, q):
+    """Rank `world - 1` leaves between two calls (no collective in flight); the others must get an
+    error from their next exchange instead of waiting for ever."""
+    import datetime
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from yamoe_b200 import ep, workloads
+    T, H, E, K = 24, 16, 6, 2
+    inp = workloads.make_inputs(T, H, E, K, seed=5, weight_std=0.3, bias_std=0.3)
+    lo, hi = rank * (T // world), (rank + 1) * (T // world)
+    local_w = ep.shard_expert_weights(*[inp[k] for k in KEYS[3:]], rank, world)
+    args = (inp["hidden_states"][lo:hi], inp["router_indices"][lo:hi], inp["routing_weights"][lo:hi], *local_w, T, E, K)
+    first = ep.ep_experts(*args, backend=cpu_backend())
+    dist.barrier()                      # the step is complete on every rank
+    if rank == world - 1:
+        q.put((rank, "left", first))
+        dist.destroy_process_group()
+        return
+    try:
+        ep.ep_experts(*args, backend=cpu_backend())
+        q.put((rank, "completed", None))
+    except Exception as exc:            # the expected outcome: a clean error on the surviving ranks
+        q.put((rank, "error", type(exc).__name__))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_rank_leaving_between_steps_gives_a_clean_error():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    world = 3
+    port = 29500 + (os.getpid() + 977) % 2000
+    procs = [ctx.Process(target=_leaver_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted((q.get(timeout=120) for _ in range(world)), key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode is not None, "a surviving rank is still waiting"
+    assert results[world - 1][1] == "left"
+    for r in results[:world - 1]:
+        assert r[1] == "error", f"rank {r[0]} {r[1]} although a peer had left"

@@ -53,18 +53,6 @@ SIGNATURES = {
     "yamoe_b200_permute_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "yamoe_b200_combine_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                                         c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
-    "yamoe_b200_ep_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
-    "yamoe_b200_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p,
-                                   c_size_t, c_void_p]),
-    "yamoe_b200_ep_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int,
-                                       c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "yamoe_b200_ep_local_forward": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "yamoe_b200_ep_return": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "yamoe_b200_ep_backward_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int]),
-    "yamoe_b200_ep_dispatch_weights": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
-                                               c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "yamoe_b200_ep_local_backward": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int, c_int,
-                                                               c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_ep_ctrl_bytes": (c_size_t, [c_int, c_int]),
     "yamoe_b200_ep_call_workspace_bytes": (c_size_t, [_ctx_p, c_int64, c_int]),
     "yamoe_b200_ep_forward": (c_int, [_ctx_p, c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 5 +
@@ -79,6 +67,9 @@ SIGNATURES = {
                                           c_int64, c_int, c_int, c_void_p]),
     "yamoe_b200_index_select": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "yamoe_b200_router_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "yamoe_b200_router_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "yamoe_b200_router_forward": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
+                                                           c_void_p]),
     "yamoe_b200_experts_forward_saving": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 5 +
                                           [c_int64, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "yamoe_b200_experts_backward_saved": (c_int, [c_void_p, c_int, c_void_p, c_int] + [c_void_p] * 9 +

@@ -1,7 +1,22 @@
-// Expert parallelism without host-side collectives: the count exchange and the two phase
-// boundaries of the peer-store path (ep_p2p.cuh) become flags in symmetric memory, so that one
-// expert-parallel call is a fixed chain of kernels on one stream and no NCCL call at all.
+// Expert parallelism over peer memory, without host-side collectives: token rows travel to the
+// expert owners and result rows back as plain stores into the other GPUs' buffers (NVLink); every
+// offset is derived on the device from the [G, E] matrix of per-rank counts, and the count exchange
+// and the phase boundaries are flags in symmetric memory, so that one expert-parallel call is a
+// fixed chain of kernels on one stream: no NCCL call, no host round trip, no split sizes.
 // The reference is single-GPU; there is no counterpart.
+//
+// Rank r owns experts [r*per, (r+1)*per) and a shard of the tokens.  Buffers that peers write
+// into (symmetric allocations, one per rank, same size everywhere):
+//   recv_x [max_rows, H]   rows of the experts this rank owns, already in the padded,
+//                          expert-sorted layout the grouped GEMMs consume: expert le starts at
+//                          pad_off[le]; inside it rows are ordered by source rank, then by the
+//                          source's stable order (= global token order, which is what the
+//                          capacity rule needs)
+//   back_y [S_local, H]    result rows of this rank's assignments, in its own sorted order
+// The backward pass travels the same way: token rows, upstream-gradient rows and one fp32 routing
+// weight per row go out with the dispatch kernel; the input-gradient rows return through the last
+// data-gradient GEMM's epilogue (EpiPeerRows without a bias) and the routing-weight gradients with
+// ep_return_scalar_kernel.
 //
 // Every rank owns a control block that its peers may write (EpCtrl, layout below).  A call has an
 // epoch number (a device counter in the rank's private state, incremented by the first kernel of
@@ -10,7 +25,7 @@
 //   ep_publish_kernel     my per-expert counts -> counts[epoch & 1][rank][:] of every peer, then
 //                         flag_counts[rank] = epoch there
 //   ep_dispatch_kernel    waits until flag_counts[s] >= epoch for every source s (bounded), derives
-//                         every offset from the [G, E] counts (as ep_plan_kernel does), stores my
+//                         every offset from the [G, E] counts, stores my
 //                         rows into the owners' receive buffers, and its last CTA sets
 //                         flag_dispatch[rank] = epoch on every peer
 //   ep_wait_kernel        one warp; waits for flag_dispatch[s] >= epoch from every source (bounded)
@@ -32,10 +47,93 @@
 // every rank (all ranks see the same counts) so that nothing is stored or computed.
 #pragma once
 #include "common.cuh"
-#include "ep_p2p.cuh"
 #include "misc_kernels.cuh"
 
 namespace yb {
+
+struct EpTables {
+  RouteTables rt;          // tables of the LOCAL problem (per experts, padded rows)
+  int32_t* dest_row;       // [E]      first row on the owner of expert e for rows sent by this rank
+  int32_t* src_start;      // [G*per]  start of expert (r*per+le) in source s's sorted order
+  int32_t* seg_row;        // [G*per]  first local row of the rows source s sent for local expert le
+  int64_t* row_dest;       // [max_rows] address of the row's slot in its source rank's back buffer, 0 for padding
+};
+
+// row_token[r] = r for kept rows, -1 for padding and for rows beyond the capacity; weight 1;
+// row_dest[r] = where the row's result goes in the peer memory of the rank it came from.
+__global__ void ep_rowtables_kernel(EpTables t, int64_t capacity, int64_t max_rows, void* const* peer_back,
+                                    int G, int per, int64_t row_bytes) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= max_rows) return;
+  int32_t tok = -1;
+  int64_t dest = 0;
+  if (r < t.rt.header[kHdrRowsUsed]) {
+    const int le = t.rt.tile_expert[r / kTileM];
+    const int64_t i = r - t.rt.pad_off[le];
+    const int64_t c = t.rt.counts[le];
+    if (i < (c < capacity ? c : capacity)) tok = (int32_t)r;
+    if (i < c && peer_back != nullptr) {
+      int s = 0;
+      while (s + 1 < G && t.seg_row[(s + 1) * per + le] <= r) ++s;
+      const int64_t dst_row = (int64_t)t.src_start[s * per + le] + (r - t.seg_row[s * per + le]);
+      dest = reinterpret_cast<int64_t>(peer_back[s]) + dst_row * row_bytes;
+    }
+  }
+  t.rt.row_token[r] = tok;
+  t.rt.row_weight[r] = 1.0f;
+  t.row_dest[r] = dest;
+}
+
+// Down-projection epilogue fused with the combine exchange: the bias-added result row goes
+// straight into the back buffer of the rank that owns the token (a peer store over NVLink);
+// rows dropped by the capacity send zeros, padding rows send nothing.
+template <typename T>
+struct EpiPeerRows {
+  const T* bias;             // [per, N], or nullptr
+  const int64_t* row_dest;
+  const int32_t* row_token;
+  int N;
+
+  template <int NV>
+  __device__ __forceinline__ void apply(int e, int row, int n0, const float (&v)[NV]) const {
+    const int64_t dest = row_dest[row];
+    if (dest == 0) return;
+    float o[NV];
+    if (row_token[row] < 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] = 0.f;
+    } else if (bias != nullptr) {
+      load_vec<T, NV>(bias + (size_t)e * N + n0, o);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] += v[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] = v[i];
+    }
+    store_vec<T, NV>(reinterpret_cast<T*>(dest) + n0, o);
+  }
+};
+
+// row_weight[r] = received routing weight for kept rows, 0 for padding and dropped rows.
+__global__ void ep_load_weights_kernel(EpTables t, const float* __restrict__ recv_w, int64_t max_rows) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= max_rows) return;
+  t.rt.row_weight[r] = t.rt.row_token[r] >= 0 ? recv_w[r] : 0.f;
+}
+
+// One thread per local row: val[row] (fp32) goes back to the rank the row came from, at the
+// position of the assignment in that rank's sorted order.  Padding rows send nothing.
+__global__ void ep_return_scalar_kernel(const float* __restrict__ val, EpTables t,
+                                        void* const* __restrict__ peer_back_w, int G, int per) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= t.rt.header[kHdrRowsUsed]) return;
+  const int le = t.rt.tile_expert[r / kTileM];
+  if (r - t.rt.pad_off[le] >= t.rt.counts[le]) return;
+  int s = 0;
+  while (s + 1 < G && t.seg_row[(s + 1) * per + le] <= r) ++s;
+  const int64_t dst_row = (int64_t)t.src_start[s * per + le] + (r - t.seg_row[s * per + le]);
+  reinterpret_cast<float*>(peer_back_w[s])[dst_row] = t.rt.row_token[r] >= 0 ? val[r] : 0.f;
+}
 
 enum EpStatus {
   kStatusEpCountsTimeout = 4,
@@ -167,7 +265,7 @@ ep_dispatch_fused_kernel(const EpDispatchArgs a, EpTables t) {
     __syncthreads();
   }
   const int bad = s_bad;
-  // ---- CTA 0: this rank's own tables (what ep_plan_kernel writes) -------------------------------
+  // ---- CTA 0: this rank's own tile tables and the (source, expert) segments for the way back ----
   if (blockIdx.x == 0) {
     if (bad != 0) {
       if (tid == 0) {

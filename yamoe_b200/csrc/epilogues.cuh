@@ -105,16 +105,20 @@ __device__ __forceinline__ void red_add_vec(float* __restrict__ dst, const float
 // reference: csrc/moe.cpp:163-180.  Emits NV/2 activation columns per call.  Padding rows are
 // written as exact zeros so that weight-gradient GEMMs may run over whole padded segments.
 // Optional outputs for the backward recompute: `pre` (biased pre-activations, [rows,2H]) and
-// `actw` (activation times routing weight).
+// `actw` (activation times routing weight).  Rows of actw are actw_ld >= H elements apart; the
+// columns behind the H activations receive (w_row, 0, 0, ...), so that the weight-gradient GEMM
+// whose transposed operand is actw also produces the down-projection bias gradient
+// sum_r w_r * grad_y[r] in its output row H (reference: csrc/experts_backward.cu:277).
 template <typename T>
 struct EpiGlu {
   const T* bias;             // [E, 2H]
   T* act;                    // [rows, H]   (may be null when only actw/pre are wanted)
-  T* actw;                   // [rows, H]   or null
+  T* actw;                   // [rows, actw_ld]   or null
   T* pre;                    // [rows, 2H]  or null
   const int32_t* row_token;
   const float* row_weight;
   int H;                     // activation columns (= N/2)
+  int actw_ld;               // row pitch of actw (0 = H)
 
   template <int NV>
   __device__ __forceinline__ void apply(int e, int row, int n0, const float (&v)[NV]) const {
@@ -149,9 +153,18 @@ struct EpiGlu {
     if (act != nullptr) store_vec<T, NV / 2>(act + (size_t)row * H + n0 / 2, a);
     if (actw != nullptr) {
       const float w = pad ? 0.f : row_weight[row];
+      const int ld = actw_ld > 0 ? actw_ld : H;
 #pragma unroll
       for (int i = 0; i < NV / 2; ++i) a[i] *= w;
-      store_vec<T, NV / 2>(actw + (size_t)row * H + n0 / 2, a);
+      store_vec<T, NV / 2>(actw + (size_t)row * ld + n0 / 2, a);
+      if (n0 == 0) {
+        // (ld - H) is a multiple of 8 and rows are 16-byte aligned: eight columns per store
+        float x[8] = {w, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = H; j < ld; j += 8) {
+          store_vec<T, 8>(actw + (size_t)row * ld + j, x);
+          x[0] = 0.f;
+        }
+      }
     }
   }
 };
@@ -248,6 +261,22 @@ struct EpiStore {
   __device__ __forceinline__ void apply(int e, int row, int n0, const float (&v)[NV]) const {
     if (row >= M) return;
     store_vec<T, NV>(C + ((size_t)e * M + row) * N + n0, v);
+  }
+};
+
+// ---- weight gradient with the bias gradient riding along ------------------------------------
+// The transposed operand of the GEMM carries one extra column (see gather_rows_kernel / EpiGlu),
+// so output row M holds the bias gradient: rows < M go to C, row M to bias_out, later rows nowhere.
+template <typename T>
+struct EpiStoreBias {
+  T* C;                      // [E, M, N]
+  T* bias_out;               // [E, N]
+  int M, N;
+
+  template <int NV>
+  __device__ __forceinline__ void apply(int e, int row, int n0, const float (&v)[NV]) const {
+    if (row < M) store_vec<T, NV>(C + ((size_t)e * M + row) * N + n0, v);
+    else if (row == M) store_vec<T, NV>(bias_out + (size_t)e * N + n0, v);
   }
 };
 

@@ -122,7 +122,43 @@ gemv_kernel(const GemvArgs g) {
     if (gtid < (size_t)nslab) g.slab_done[gtid] = 0;
   }
   // ---- routing, rebuilt per CTA ---------------------------------------------------------------
-  for (int e = tid; e < g.E; e += kGemvThreads) cnt[e] = 0;
+  int e;
+  if (g.S <= 32) {
+    // At most one assignment per lane: warp 0 sorts with ballots, no shared-memory histogram and
+    // a single barrier.  (At T = 1 the set-up of a CTA is a visible share of its 10 us of streaming.)
+    if (w == 0) {
+      int my = -1;
+      if (lane < g.S) {
+        const int64_t v = g.router_indices[lane];
+        if (v >= 0 && v < g.E) my = (int)v;
+      }
+      const unsigned valid = __ballot_sync(0xffffffffu, my >= 0);
+      const unsigned same = __match_any_sync(0xffffffffu, my);
+      const bool first = my >= 0 && (__ffs(same) - 1) == lane;     // first assignment of its expert
+      // rank of my expert among the touched ones, ascending
+      int rank = 0;
+      for (int o = 0; o < 32; ++o) {
+        const int oe = __shfl_sync(0xffffffffu, my, o);
+        const int of = __shfl_sync(0xffffffffu, (int)first, o);
+        if (of && oe < my) ++rank;
+      }
+      const unsigned firsts = __ballot_sync(0xffffffffu, first);
+      const unsigned pick = __ballot_sync(0xffffffffu, first && rank == (int)blockIdx.x);
+      int mine_e = -1;
+      if (pick) mine_e = __shfl_sync(0xffffffffu, my, __ffs(pick) - 1);
+      const unsigned members = __ballot_sync(0xffffffffu, my >= 0 && my == mine_e) & valid;
+      if (my >= 0 && my == mine_e) rows[__popc(members & ((1u << lane) - 1u))] = lane;   // stable: ascending p
+      if (lane == 0) {
+        s_my_e = mine_e;
+        s_touched = __popc(firsts);
+        s_warp[0] = __popc(members);
+      }
+    }
+    __syncthreads();
+    e = s_my_e;
+    if (e < 0) return;                    // fewer touched experts than grid slots
+  } else {
+  for (int ee = tid; ee < g.E; ee += kGemvThreads) cnt[ee] = 0;
   if (tid == 0) { s_my_e = -1; s_touched = 0; }
   __syncthreads();
   int my = -1;
@@ -158,7 +194,7 @@ gemv_kernel(const GemvArgs g) {
     if (tid == kGemvThreads - 1) s_touched = rank;   // last thread ends on the total
     __syncthreads();
   }
-  const int e = s_my_e;
+  e = s_my_e;
   if (e < 0) return;                      // fewer touched experts than grid slots
   {
     // stable list of this expert's assignments
@@ -171,11 +207,9 @@ gemv_kernel(const GemvArgs g) {
     if (mine) rows[base + __popc(bal & ((1u << lane) - 1u))] = tid;
     __syncthreads();
   }
-  const int n_all = cnt[e];
+  }
+  const int n_all = g.S <= 32 ? s_warp[0] : cnt[e];
   const int n_rows = (int64_t)n_all < g.capacity ? n_all : (int)g.capacity;
-  // everything above read only the caller's inputs; below come act / out32 / slab counters
-  if constexpr (STAGE == kDown) pdl_wait();
-
   const int n0 = blockIdx.y * NB;
   const int cg = lane % LPR;
   const int n = n0 + cg * 8;
@@ -189,6 +223,8 @@ gemv_kernel(const GemvArgs g) {
     klen = min((int)kchunk, g.Kdim - k0);
   }
   const __nv_bfloat16* wp = g.W + ((size_t)e * g.Kdim + k0) * g.N + n;
+  // everything above read only the caller's inputs; below come act / out32 / slab counters
+  if constexpr (STAGE == kDown) pdl_wait();
   const int part = w * RPW + lane / LPR;
 
   for (int r0 = 0; r0 < n_rows; r0 += kGemvMT) {

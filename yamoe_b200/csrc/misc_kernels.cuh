@@ -9,12 +9,16 @@ namespace yb {
 
 constexpr int kRowWarps = 8;  // rows per CTA in the warp-per-row kernels
 
-// dst[row, :] = src[row_token[row], :], zeros for padding rows.  One warp per row, 16-byte
+// dst[row, 0:H] = src[row_token[row], :], zeros for padding rows.  One warp per row, 16-byte
 // accesses.  reference: csrc/gather.cu:6-66 (which writes a padded [E,C,H] buffer instead).
+// Rows of dst are dst_ld elements apart; when dst_ld > H the columns behind the copy get
+// (1, 0, 0, ...) for token rows and zeros for padding rows: a weight-gradient GEMM that takes dst as
+// its transposed operand then yields, in output row H, the column sums of its other operand
+// (the bias gradient, reference: csrc/experts_backward.cu:308).
 template <typename T>
 __global__ void __launch_bounds__(kRowWarps * 32)
 gather_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, const int32_t* __restrict__ row_token,
-                   const int32_t* __restrict__ header, int H) {
+                   const int32_t* __restrict__ header, int H, int dst_ld) {
   pdl_wait();
   pdl_trigger();
   const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
@@ -22,13 +26,14 @@ gather_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, const int32_t
   const int lane = threadIdx.x & 31;
   const int tok = row_token[row];
   const int nvec = H * (int)sizeof(T) / 16;
-  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)row * H);
+  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)row * dst_ld);
   if (tok < 0) {
     for (int i = lane; i < nvec; i += 32) d[i] = make_uint4(0, 0, 0, 0);
   } else {
     const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)tok * H);
     for (int i = lane; i < nvec; i += 32) d[i] = __ldg(s + i);
   }
+  for (int j = H + lane; j < dst_ld; j += 32) DT<T>::st(dst + (size_t)row * dst_ld + j, (j == H && tok >= 0) ? 1.f : 0.f);
 }
 
 // Backward gather: gys[row, :] = grad_y[token, :] where grad_y is grad_out, or the sum of its K

@@ -34,6 +34,9 @@ struct GemmArgs {
   // is source row gather_rows[r] (negative = padding), fetched by TMA gather
   const int32_t* gather_rows = nullptr;
   int64_t gather_src_rows = 0;
+  // row-tiled arrangements without tables (tile_expert == nullptr): one group (expert 0) owns the
+  // a_rows rows of A; rows at and beyond a_rows read as zeros
+  int64_t a_rows = 0;
 };
 
 constexpr int kSimtBN = 128, kSimtBK = 16, kSimtThreads = 256;
@@ -76,8 +79,13 @@ simt_gemm_kernel(GemmArgs g, Epi epi) {
     m_limit = g.M;
   } else {
     row0 = blockIdx.y * BM;                 // padded row
-    if (row0 >= g.header[kHdrRowsUsed]) return;
-    e = g.tile_expert[row0 / kTileM];
+    if (g.tile_expert == nullptr) {
+      if (row0 >= g.a_rows) return;
+      e = 0;
+    } else {
+      if (row0 >= g.header[kHdrRowsUsed]) return;
+      e = g.tile_expert[row0 / kTileM];
+    }
     k_begin = 0;
     k_end = g.K;
     m_limit = row0 + BM;
@@ -110,7 +118,8 @@ simt_gemm_kernel(GemmArgs g, Epi epi) {
       simt_load<T, RT>(A + (size_t)k * g.lda + m, k < k_end && m < m_limit, vec_a, ra);
     } else {
       const int k = k0 + ak_k;
-      simt_load<T, RT>(A + (size_t)(row0 + ak_row) * g.lda + k, k < k_end, vec_a, ra);
+      simt_load<T, RT>(A + (size_t)(row0 + ak_row) * g.lda + k, k < k_end && (g.a_rows == 0 || row0 + ak_row < g.a_rows),
+                       vec_a, ra);
     }
     if constexpr (MODE == kDgrad) {
       const int k = k0 + bk_k, n = n0 + bk_n;

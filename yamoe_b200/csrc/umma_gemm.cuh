@@ -185,8 +185,9 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
 
 struct UmmaParams {
   int M, N, K, E;           // as GemmArgs
-  const int32_t* tile_expert;
+  const int32_t* tile_expert;   // null: one group (expert 0) owns all `uniform_tiles` row tiles, no tables
   const int32_t* pad_off;
+  int uniform_tiles;
   int32_t* header;
   const int32_t* gather_rows;   // kFwd: source row of every padded row (TMA gather of A), or null
 };
@@ -243,9 +244,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // previous kernel has completed before touching anything it produced.
   pdl_trigger();
   pdl_wait();
-  const bool pad_in_smem = p.E <= kUmmaMaxExperts;
+  const bool uniform = p.tile_expert == nullptr && MODE != kWgrad;
+  const bool pad_in_smem = uniform || p.E <= kUmmaMaxExperts;
   if (pad_in_smem) {
-    for (int i = threadIdx.x; i <= p.E; i += kUmmaThreads) s_pad[i] = p.pad_off[i];
+    if (uniform) {
+      if (threadIdx.x == 0) { s_pad[0] = 0; s_pad[1] = p.uniform_tiles * kTileM; }
+    } else {
+      for (int i = threadIdx.x; i <= p.E; i += kUmmaThreads) s_pad[i] = p.pad_off[i];
+    }
     __syncthreads();
   }
   const int32_t* pad = pad_in_smem ? s_pad : p.pad_off;
@@ -258,12 +264,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     MT = (p.M + kUmmaBM - 1) / kUmmaBM;
     total = p.E * MT * NT;
   } else {
-    total = p.header[kHdrRowTiles] * NT;
+    total = (uniform ? p.uniform_tiles : p.header[kHdrRowTiles]) * NT;
   }
   // Expert of tile `id` for the row-tiled arrangements: the only part of a tile's description
   // that comes from global memory.  Every role asks for it one tile ahead.
   auto expert_of = [&](int id) -> int {
     if constexpr (MODE == kWgrad) return 0;
+    if (uniform) return 0;
     return id < total ? __ldg(p.tile_expert + id / NT) : 0;
   };
   auto decode = [&](int id, int e_hint, int& e, int& row0, int& n0, int& kb_begin_row, int& kblocks) {
@@ -622,7 +629,7 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
       return YAMOE_ERR_CUDA;
     attr_done = true;
   }
-  UmmaParams p{g.M, g.N, g.K, g.E, g.tile_expert, g.pad_off, const_cast<int32_t*>(g.header),
+  UmmaParams p{g.M, g.N, g.K, g.E, g.tile_expert, g.pad_off, (int)max_tiles, const_cast<int32_t*>(g.header),
                MODE == kFwd ? g.gather_rows : nullptr};
   const int NT = (int)ceil_div(g.N, BN);
   int64_t total_max = MODE == kWgrad ? (int64_t)g.E * ceil_div(g.M, kUmmaBM) * NT : max_tiles * NT;

@@ -83,7 +83,8 @@ class Yamoe(torch.nn.Module):
       the token count) for a run that never drops and therefore matches `GptOssMLP`.
     * gradients are not switched off: when autograd is recording, the router runs in PyTorch and
       the experts go through `_ExpertsFn`, so router and expert weights receive gradients.  Without
-      autograd the top-k / softmax / scatter run in one CUDA kernel.
+      autograd the whole router (projection, top-k, softmax, scatter) runs in the library: one
+      tcgen05 kernel for bf16.
     """
     can_torch_compile: bool = False
 
@@ -93,15 +94,16 @@ class Yamoe(torch.nn.Module):
         E = getattr(self, "num_experts", self.router.weight.shape[0])
         K = getattr(self, "top_k", 4)
         x = hidden_states.reshape(T, hidden)
-        logits = torch.nn.functional.linear(x, self.router.weight, self.router.bias)
         needs_grad = torch.is_grad_enabled() and (
             x.requires_grad or self.router.weight.requires_grad or self.experts.gate_up_proj.requires_grad)
         if needs_grad:
+            logits = torch.nn.functional.linear(x, self.router.weight, self.router.bias)
             top_v, router_indices = torch.topk(logits, K, dim=-1)
             top_w = torch.nn.functional.softmax(top_v, dim=-1, dtype=top_v.dtype)
             router_scores = torch.zeros_like(logits).scatter(1, router_indices, top_w)
         else:
-            router_indices, router_scores = ops.router_topk(logits, K)
+            # router projection, top-k, softmax and scatter in the library (one kernel for bf16)
+            router_indices, router_scores = ops.router_forward(x, self.router.weight, self.router.bias, K)
         cap = getattr(self, "expert_capacity", None)
         if cap is None:
             cap = ceil_div(T * K, E)

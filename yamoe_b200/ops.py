@@ -378,6 +378,33 @@ def router_topk(router_logits: torch.Tensor, top_k: int):
     return idx, scores
 
 
+def router_forward(hidden_states: torch.Tensor, router_weight: torch.Tensor, router_bias, top_k: int):
+    """(router_indices [T,K] int64, router_scores [T,E]) straight from the layer input: router
+    projection, top-k, softmax over the k selected logits and dense scatter
+    (torch-ext/yamoe/layers.py:126-149).  One kernel for bf16 (tcgen05 GEMM with the top-k in its
+    epilogue); the CUDA-core GEMM plus the top-k kernel otherwise."""
+    _require(hidden_states.is_cuda and hidden_states.dim() == 2 and hidden_states.dtype in _DT,
+             "router_forward: 2D CUDA float32/bfloat16 hidden_states expected")
+    _require(router_weight.dim() == 2 and router_weight.shape[1] == hidden_states.shape[1]
+             and router_weight.dtype == hidden_states.dtype, "router_forward: router weight must be [E, H] of the same dtype")
+    x, w = hidden_states.contiguous(), router_weight.contiguous()
+    b = router_bias.contiguous() if router_bias is not None else None
+    _require(b is None or (b.dtype == x.dtype and b.numel() == w.shape[0]), "router_forward: bias must be [E] of the same dtype")
+    T, H = x.shape
+    E = w.shape[0]
+    idx = torch.empty(T, int(top_k), dtype=torch.int64, device=x.device)
+    scores = torch.empty(T, E, dtype=x.dtype, device=x.device)
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        ws = _workspace(L.yamoe_b200_router_workspace_bytes(T, E), x.device)
+        st = L.yamoe_b200_router_forward(x.data_ptr(), w.data_ptr(), b.data_ptr() if b is not None else None,
+                                         idx.data_ptr(), scores.data_ptr(), T, H, E, int(top_k), _DT[x.dtype],
+                                         ws.data_ptr(), ws.numel(), _stream())
+        _lib.check(st, "router_forward")
+        _check_device_status(ws, "router_forward")
+    return idx, scores
+
+
 experts = torch.ops.yamoe_b200.experts
 batch_mm = torch.ops.yamoe_b200.batch_mm
 experts_backward = torch.ops.yamoe_b200.experts_backward
