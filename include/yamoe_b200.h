@@ -55,7 +55,10 @@ int yamoe_b200_set_path(int path);
 
 /* Profiling aid, process-wide and not thread-safe: while `stage` is non-zero, every forward call
  * records `start_event` / `stop_event` (cudaEvent_t) on its stream immediately before / after
- * the kernels of that stage: 1 gate_up GEMM, 2 down GEMM, 3 routing, 4 row gather; 0 disables. */
+ * the kernels of that stage: 1 gate_up GEMM, 2 down GEMM, 3 routing, 4 row gather, 5 the
+ * expert-parallel call up to the arrival of all rows (local sort, count exchange, dispatch, wait),
+ * 6 its end (return signal, wait for all owners, combine), 7 the combine of the single-GPU forward;
+ * 0 disables.  The same stages are NVTX ranges ("yamoe_b200:<stage>") on the calling thread. */
 int yamoe_b200_set_stage_events(void *start_event, void *stop_event, int stage);
 
 /* ---------------------------------------------------------------------------------------------

@@ -60,6 +60,45 @@ def test_router_topk_kernel():
 
 
 @pytest.mark.gpu
+def test_router_forward_matches_linear_topk_softmax():
+    """Router projection + top-k + softmax + scatter in the library against the reference layer's
+    chain (torch-ext/yamoe/layers.py:126-149) in torch: fp32 through the CUDA-core GEMM and the top-k
+    kernel, bf16 through the single tcgen05 kernel (H a multiple of 64) and through the two-kernel
+    form (H = 72)."""
+    import yamoe_b200
+    for T, H, E, K, dtype in ((300, 256, 32, 4, torch.float32), (1, 128, 8, 2, torch.float32),
+                              (1000, 2880, 32, 4, torch.bfloat16), (130, 256, 128, 4, torch.bfloat16),
+                              (5, 128, 48, 3, torch.bfloat16), (64, 72, 16, 2, torch.bfloat16)):
+        gen = torch.Generator().manual_seed(T + E)
+        x = torch.randn(T, H, generator=gen).to(dtype)
+        w = (torch.randn(E, H, generator=gen) / H ** 0.5).to(dtype)
+        b = (torch.randn(E, generator=gen) * 0.1).to(dtype)
+        idx, scores = yamoe_b200.router_forward(x.cuda(), w.cuda(), b.cuda(), K)
+        idx, scores = idx.cpu(), scores.float().cpu()
+        logits = torch.nn.functional.linear(x.cuda(), w.cuda(), b.cuda()).float().cpu()     # same dtype rounding
+        top_v, ref_idx = torch.topk(logits, K, dim=-1)
+        assert ((idx >= 0) & (idx < E)).all()
+        if dtype == torch.float32:
+            # selections agree wherever the k-th and (k+1)-th logits are not within rounding of each other
+            sorted_v = logits.sort(dim=1, descending=True).values
+            clear = (sorted_v[:, K - 1] - sorted_v[:, K]) > 1e-5 if E > K else torch.ones(T, dtype=torch.bool)
+            assert torch.equal(idx[clear].sort(1).values, ref_idx[clear].sort(1).values)
+            tol = 2e-5
+        else:
+            # bf16 logits tie often and the accumulation order differs from cuBLAS by an ulp here and
+            # there: compare the selected logit values and the scores, not the ids
+            got_v = torch.gather(logits, 1, idx)
+            assert (got_v.sort(1, descending=True).values - top_v).abs().max() <= 2e-2 * logits.abs().max()
+            tol = 2e-2
+        ref_scores = torch.zeros(T, E).scatter_(1, ref_idx, torch.softmax(top_v, -1))
+        got_sorted = scores.sort(dim=1, descending=True).values[:, :K]
+        ref_sorted = ref_scores.sort(dim=1, descending=True).values[:, :K]
+        assert (got_sorted - ref_sorted).abs().max() <= tol, (T, H, E, K, dtype)
+        assert int((scores != 0).sum(1).max()) <= K
+        assert ((scores.sum(1) - 1).abs() <= 2e-2).all()
+
+
+@pytest.mark.gpu
 def test_router_topk_non_finite_logits():
     """NaN rows and rows with fewer than K finite logits: every selected id must be a valid expert
     and nothing may be written outside the [T, E] score row, as with torch.topk."""

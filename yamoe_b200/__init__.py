@@ -3,7 +3,7 @@ the reference's operator interface (torch-ext/yamoe/__init__.py:6-12)."""
 from . import _lib
 from .layers import Yamoe, _ExpertsFn, experts_autograd
 from .ops import (batch_mm, batch_mm_wgrad, bincount_cumsum, experts, experts_backward, gather, index_select_out,
-                  route, router_topk, scatter, sort)
+                  route, router_forward, router_topk, scatter, sort)
 
 
 def set_path(name: str) -> str:
@@ -14,4 +14,4 @@ def set_path(name: str) -> str:
 
 
 __all__ = ["experts", "experts_backward", "sort", "bincount_cumsum", "gather", "scatter", "index_select_out", "route",
-           "batch_mm", "batch_mm_wgrad", "experts_autograd", "Yamoe", "router_topk", "_ExpertsFn", "set_path"]
+           "batch_mm", "batch_mm_wgrad", "experts_autograd", "Yamoe", "router_topk", "router_forward", "_ExpertsFn", "set_path"]

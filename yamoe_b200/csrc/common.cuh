@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <stdint.h>
 
 #include <atomic>
@@ -148,16 +149,29 @@ struct StageEvents {
   std::atomic<void*> start{nullptr}, stop{nullptr};
 };
 inline StageEvents g_events;
-enum Stage { kStageNone = 0, kStageGateUp = 1, kStageDown = 2, kStageRoute = 3, kStageGather = 4 };
+enum Stage { kStageNone = 0, kStageGateUp = 1, kStageDown = 2, kStageRoute = 3, kStageGather = 4,
+             kStageEpDispatch = 5, kStageEpCombine = 6, kStageCombine = 7, kStageLast = 7 };
 
+inline const char* stage_name(int stage) {
+  static const char* const names[] = {"yamoe_b200", "yamoe_b200:gate_up", "yamoe_b200:down", "yamoe_b200:route",
+                                      "yamoe_b200:gather", "yamoe_b200:ep_dispatch", "yamoe_b200:ep_combine",
+                                      "yamoe_b200:combine"};
+  return names[stage >= 0 && stage <= kStageLast ? stage : 0];
+}
+
+// Brackets the launches of one stage: an NVTX range on the host thread (a no-op unless a profiler
+// that listens to NVTX is attached) and, when the stage was selected with
+// yamoe_b200_set_stage_events, the caller's two events on the stream.
 struct StageTimer {
   bool on;
   cudaStream_t st;
   StageTimer(int stage, cudaStream_t s) : on(g_events.stage.load() == stage && g_events.start.load()), st(s) {
+    nvtxRangePushA(stage_name(stage));
     if (on) cudaEventRecord(reinterpret_cast<cudaEvent_t>(g_events.start.load()), st);
   }
   ~StageTimer() {
     if (on) cudaEventRecord(reinterpret_cast<cudaEvent_t>(g_events.stop.load()), st);
+    nvtxRangePop();
   }
 };
 

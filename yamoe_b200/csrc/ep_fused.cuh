@@ -86,13 +86,33 @@ __global__ void ep_rowtables_kernel(EpTables t, int64_t capacity, int64_t max_ro
 
 // Down-projection epilogue fused with the combine exchange: the bias-added result row goes
 // straight into the back buffer of the rank that owns the token (a peer store over NVLink);
-// rows dropped by the capacity send zeros, padding rows send nothing.
+// rows dropped by the capacity send zeros, padding rows send nothing.  In the tcgen05 kernel the
+// rows leave in 128-byte pieces (kStagedRows), which is what makes the NVLink stores efficient.
 template <typename T>
 struct EpiPeerRows {
+  static constexpr bool kStagedRows = sizeof(T) == 2;
+  static constexpr int kOutPerChunk = 32;
   const T* bias;             // [per, N], or nullptr
   const int64_t* row_dest;
   const int32_t* row_token;
   int N;
+
+  __device__ __forceinline__ T* row_ptr(int row) const { return reinterpret_cast<T*>(row_dest[row]); }
+
+  template <int NV>
+  __device__ __forceinline__ void values(int e, int row, int n0, const float (&v)[NV], float (&o)[NV]) const {
+    if (row_token[row] < 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] = 0.f;
+    } else if (bias != nullptr) {
+      load_vec<T, NV>(bias + (size_t)e * N + n0, o);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] += v[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) o[i] = v[i];
+    }
+  }
 
   template <int NV>
   __device__ __forceinline__ void apply(int e, int row, int n0, const float (&v)[NV]) const {

@@ -27,6 +27,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "epilogues.cuh"
@@ -183,6 +184,21 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
   return d;
 }
 
+// Epilogue functors that declare `static constexpr bool kStagedRows = true` get their output rows
+// written in 128-byte pieces: a warp parks two 32-column chunks of its 32 rows in shared memory
+// (bf16), then stores them so that eight lanes cover 128 contiguous bytes of one row.  Plain
+// functors store 16 bytes per lane to 32 different rows per instruction, which local memory
+// tolerates (L2 merges the pieces) but which wastes most of every NVLink packet when the row lives
+// in another GPU's memory.  Such a functor provides, besides apply():
+//   kOutPerChunk                                    32, or 16 for a functor that turns column pairs into one value
+//   T* row_ptr(int row) const                       start of the output row, or nullptr to skip it
+//   values<32>(e, row, n0, v, o) const              o[0 .. kOutPerChunk) = the outputs of accumulator columns n0 .. n0+31
+template <class E, class = void>
+struct epi_staged : std::false_type {};
+template <class E>
+struct epi_staged<E, std::enable_if_t<E::kStagedRows>> : std::true_type {};
+constexpr int kStagePitch = 144;    // bytes per parked row: 64 bf16 + 16 bytes against bank conflicts
+
 struct UmmaParams {
   int M, N, K, E;           // as GemmArgs
   const int32_t* tile_expert;   // null: one group (expert 0) owns all `uniform_tiles` row tiles, no tables
@@ -215,6 +231,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int32_t s_pad[kUmmaMaxExperts + 1];   // copy of pad_off[0..E]
+  constexpr bool kStaged = epi_staged<Epi>::value;
+  __shared__ __align__(16) uint8_t s_out[kStaged ? 4 * 32 * kStagePitch : 16];   // parked output rows, per epilogue warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -494,6 +512,56 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int nchunks = min(BN / 32, (p.N - n0 + 31) / 32);
       uint32_t ra[32], rb[32];
       tc_ld_32x32_issue(t_row, ra);
+      if constexpr (kStaged) {
+        constexpr int OUT = Epi::kOutPerChunk;                            // output columns per 32-column chunk
+        constexpr int CPP = 64 / OUT;                                     // chunks that fill a parked 128-byte row
+        constexpr int DIV = 32 / OUT;                                     // accumulator columns per output column
+        uint8_t* mine = s_out + (q * 32 + lane) * kStagePitch;            // this thread's parked row
+        const unsigned long long my_dst = reinterpret_cast<unsigned long long>(epi.row_ptr(row));
+        const int piece = lane & 7, sub = lane >> 3;                      // 16-byte piece of a row, row within a group of 4
+        const int n_out = p.N / DIV;
+        auto park = [&](const uint32_t (&r)[32], int c) {
+          float v[32], o[OUT];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          epi.template values<32>(e, row, n0 + c * 32, v, o);
+          uint4* dst = reinterpret_cast<uint4*>(mine + (c % CPP) * OUT * 2);
+#pragma unroll
+          for (int i = 0; i < OUT / 8; ++i)
+            dst[i] = make_uint4(pack_bf16x2(o[8 * i], o[8 * i + 1]), pack_bf16x2(o[8 * i + 2], o[8 * i + 3]),
+                                pack_bf16x2(o[8 * i + 4], o[8 * i + 5]), pack_bf16x2(o[8 * i + 6], o[8 * i + 7]));
+        };
+        auto flush = [&](int c_last) {                                    // parked chunks end with chunk c_last
+          __syncwarp();
+          const int col0 = (n0 + (c_last - c_last % CPP) * 32) / DIV;     // first output column of the parked piece
+          const int ncol = min((c_last % CPP + 1) * OUT, n_out - col0);   // columns parked and present
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + sub;                                    // row of the warp's 32
+            const unsigned lo = __shfl_sync(0xffffffffu, (unsigned)(my_dst & 0xffffffffull), r);
+            const unsigned hi = __shfl_sync(0xffffffffu, (unsigned)(my_dst >> 32), r);
+            const unsigned long long dst = ((unsigned long long)hi << 32) | lo;
+            if (dst != 0 && piece * 8 < ncol) {
+              const uint4 val = *reinterpret_cast<const uint4*>(s_out + (q * 32 + r) * kStagePitch + piece * 16);
+              *reinterpret_cast<uint4*>(dst + (size_t)(col0 + piece * 8) * 2) = val;
+            }
+          }
+          __syncwarp();
+        };
+#pragma unroll 1
+        for (int c = 0; c < nchunks; c += 2) {
+          tc_ld_wait(ra);
+          if (c + 1 < nchunks) tc_ld_32x32_issue(t_row + (c + 1) * 32, rb);
+          park(ra, c);
+          if (c % CPP == CPP - 1 || c + 1 == nchunks) flush(c);
+          if (c + 1 < nchunks) {
+            tc_ld_wait(rb);
+            if (c + 2 < nchunks) tc_ld_32x32_issue(t_row + (c + 2) * 32, ra);
+            park(rb, c + 1);
+            if ((c + 1) % CPP == CPP - 1 || c + 2 == nchunks) flush(c + 1);
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < nchunks; c += 2) {
         tc_ld_wait(ra);
@@ -512,6 +580,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rb[i]);
           epi.template apply<32>(e, row, n0 + (c + 1) * 32, v);
         }
+      }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&bar_tmem_empty[acc]));

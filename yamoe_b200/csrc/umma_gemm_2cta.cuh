@@ -10,9 +10,12 @@
 //
 // Signals:  both producers post their transaction bytes on the LEADER's full barrier
 // (cp.async.bulk.tensor ... .cta_group::2 with the leader's barrier address); the leader's MMA
-// thread frees a stage / publishes an accumulator with two tcgen05.commit, one to its own
-// barrier and one to the peer's (mapa address); the 2 x 128 epilogue threads of the pair arrive
-// on the leader's accumulator-empty barrier.  Work items are (expert, column tile, pair of row
+// thread frees a stage / publishes an accumulator with ONE tcgen05.commit to its own barrier, and
+// the leader thread that waits on that barrier anyway (its producer lane for a stage, a lane of
+// its first epilogue warp for an accumulator) passes the news on with a plain remote
+// mbarrier.arrive.  (A second commit aimed at the peer's barrier measured about 45 clocks of
+// tensor-pipe time per k-block.)  The 2 x 128 epilogue threads of the pair arrive on the leader's
+// accumulator-empty barrier.  Work items are (expert, column tile, pair of row
 // tiles); an expert with an odd number of row tiles ends with a pair whose second half is
 // computed on stale operands and discarded.  Every wait is bounded as in umma_gemm.cuh.
 #pragma once
@@ -152,6 +155,7 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       long long prof_empty = 0;
       (void)prof_empty;
+      int fills = 0;                       // k-blocks issued so far (saturating use: compared with the ring size)
       int e_next = expert_of(cluster_id);
       for (int id = cluster_id; id < total && ok; id += n_clusters) {
         int e, row0, n0;
@@ -171,6 +175,11 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             break;
           }
           YB_PROF_ADD(prof_empty)
+          // the leader's barrier was released by the MMA thread's commit: tell the peer's producer.
+          // (Not during the first trip round the ring, where every stage is free from the start and
+          // the waits on both sides pass without any arrival.)
+          if (leader && fills >= kU2Stages) mbar_arrive_cluster(mapa_u32(smem_u32(&bar_empty[stage]), 1));
+          if (fills < kU2Stages) ++fills;
           const uint32_t full = mapa_u32(smem_u32(&bar_full[stage]), 0);
           const uint32_t sa = smem_base + stage * kU2StageBytes;
           const uint32_t sb = sa + kU2ABytes;
@@ -227,14 +236,11 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           for (int k = 0; k < kUmmaBK / 16; ++k)
             tc2_mma_bf16(d_tmem, adesc + (uint64_t)(k * a_kstep), bdesc + (uint64_t)(k * b_kstep), idesc,
                          (uint32_t)((kb | k) != 0));
-          // free the stage in both CTAs
-          tc2_commit(smem_u32(&bar_empty[stage]));
-          tc2_commit(mapa_u32(smem_u32(&bar_empty[stage]), 1));
+          tc2_commit(smem_u32(&bar_empty[stage]));     // frees the stage here; the producer forwards it
           if (++stage == kU2Stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc2_commit(smem_u32(&bar_tmem_full[acc]));
-        tc2_commit(mapa_u32(smem_u32(&bar_tmem_full[acc]), 1));
+        tc2_commit(smem_u32(&bar_tmem_full[acc]));     // the leader's epilogue forwards it to the peer
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -267,6 +273,8 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         atomicMax(p.header + kHdrStatus, (int)kStatusEpilogueTimeout);
         break;
       }
+      // the accumulator is complete in both CTAs: one lane of the leader tells the peer's epilogue
+      if (leader && warp == 2 && lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bar_tmem_full[acc]), 1));
       tc_fence_after();
       if (leader || has1) {
         const uint32_t t_row = tmem_base + acc * kUmmaAccStride + ((uint32_t)(q * 32) << 16);

@@ -213,8 +213,7 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
                    (const int32_t*)p.rt.row_token, (const int32_t*)p.rt.header, H, H) != cudaSuccess)
       return YAMOE_ERR_CUDA;
   }
-  EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), reinterpret_cast<T*>(p.act), nullptr, nullptr,
-                p.rt.row_token, p.rt.row_weight, H, 0};
+  EpiGluAct<T> glu{reinterpret_cast<const T*>(bgu), reinterpret_cast<T*>(p.act), p.rt.row_token, H};
   EpiScatterAdd<T, true, true> comb{reinterpret_cast<const T*>(bd), acc, p.rt.row_token, p.rt.row_weight, H};
   GemmArgs g1{p.xs, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, E,
               p.rt.tile_expert, p.rt.pad_off, p.rt.header};
@@ -241,6 +240,7 @@ static int forward_impl(const void* hidden, const int64_t* ridx, const void* rw,
         rc = launch_umma<kFwd>(g2, wrows, p.max_rows, p.max_tiles, st);
       }
       if (rc) return rc;
+      StageTimer tm(kStageCombine, st);
       if (launch_pdl(combine_padded_kernel<T>, dim3((unsigned)ceil_div(Tn, kRowWarps)), dim3(kRowWarps * 32), 0, st,
                      reinterpret_cast<const T*>(p.yrows), (const int32_t*)p.rt.flat_row, reinterpret_cast<T*>(out),
                      Tn, H, K) != cudaSuccess)
@@ -507,8 +507,7 @@ static int ep_local_forward_impl(const void* recv_x, const void* wgu, const void
                                  const EpPlan& p, cudaStream_t st) {
   const RouteTables& rt = p.t.rt;
   const int64_t max_tiles = max_rows / kTileM;
-  EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), reinterpret_cast<T*>(p.act), nullptr, nullptr, rt.row_token,
-                rt.row_weight, H, 0};
+  EpiGluAct<T> glu{reinterpret_cast<const T*>(bgu), reinterpret_cast<T*>(p.act), rt.row_token, H};
   EpiWeightedRows<T> wrows{reinterpret_cast<const T*>(bd), reinterpret_cast<T*>(yrows), rt.row_token,
                            rt.row_weight, H};
   EpiPeerRows<T> prows{reinterpret_cast<const T*>(bd), p.t.row_dest, rt.row_token, H};
@@ -691,12 +690,17 @@ static int ep_forward_impl(const yamoe_ep_ctx_t& c, const void* hidden, const in
   const EpCallPlan p = plan_ep_call(ws, c, Tn, false);
   const EpCtrlLayout lay{c.G, c.E};
   const uint64_t wait_ns = c.wait_ns ? c.wait_ns : kWaitLimitNs;
-  int rc = ep_call_prologue<T>(c, p, hidden, nullptr, ridx, rw, rcols, Tn, cap, c.peer_back, st);
+  int rc;
+  {
+    StageTimer tm(kStageEpDispatch, st);
+    rc = ep_call_prologue<T>(c, p, hidden, nullptr, ridx, rw, rcols, Tn, cap, c.peer_back, st);
+  }
   if (rc) return rc;
   // gate_up + GLU + down on the received rows; the down GEMM's epilogue stores every result row
   // into the back buffer of the rank that owns the token
   rc = ep_local_forward_impl<T>(c.recv_x, wgu, bgu, wd, bd, nullptr, c.max_rows, c.H, c.E / c.G, c.dtype, p.ep, st);
   if (rc) return rc;
+  StageTimer tm(kStageEpCombine, st);
   ep_signal_kernel<<<1, 32, 0, st>>>(c.peer_ctrl, lay.flag_return(), c.G, c.rank,
                                      reinterpret_cast<const int32_t*>(c.state));
   const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div(Tn, kRowWarps), (int64_t)umma_sm_count() * 8));
@@ -801,7 +805,7 @@ int yamoe_b200_set_path(int path) {
 }
 
 int yamoe_b200_set_stage_events(void* start_event, void* stop_event, int stage) {
-  if (stage < kStageNone || stage > kStageGather) return YAMOE_ERR_BAD_ARG;
+  if (stage < kStageNone || stage > kStageLast) return YAMOE_ERR_BAD_ARG;
   if (stage != kStageNone && (!start_event || !stop_event)) return YAMOE_ERR_BAD_ARG;
   g_events.stage.store(kStageNone);
   g_events.start.store(start_event);

@@ -14,16 +14,36 @@ from . import _lib
 
 _DT = {torch.float32: _lib.YAMOE_F32, torch.bfloat16: _lib.YAMOE_BF16}
 
-torch.library.define(
-    "yamoe_b200::experts",
-    "(Tensor hidden_states, Tensor router_indices, Tensor routing_weights, Tensor gate_up_proj, "
-    "Tensor gate_up_proj_bias, Tensor down_proj, Tensor down_proj_bias, int expert_capacity, "
-    "int num_experts, int top_k) -> Tensor")
-torch.library.define(
-    "yamoe_b200::experts_backward",
-    "(Tensor grad_out, Tensor hidden_states, Tensor router_indices, Tensor routing_weights, "
-    "Tensor gate_up_proj, Tensor gate_up_proj_bias, Tensor down_proj, Tensor down_proj_bias, "
-    "int expert_capacity, int num_experts, int top_k) -> Tensor[]")
+
+
+def _load_cpp_binding() -> bool:
+    """`experts` and `experts_backward` come from the C++ binding (csrc/torch_binding.cpp, built as
+    libyamoe_b200_torch.so next to the CUDA library) when it is there: same schemas, same checks, a
+    dispatch that costs a few microseconds instead of some tens.  YAMOE_B200_PY_BINDING=1 keeps the
+    Python registration below (used by the tests that compare the two)."""
+    if os.environ.get("YAMOE_B200_PY_BINDING", "0") not in ("", "0"):
+        return False
+    from .build import BINDING_PATH
+    if not os.path.exists(BINDING_PATH):
+        return False
+    _lib.lib()                       # the CUDA library must be loaded first (and must exist)
+    torch.ops.load_library(BINDING_PATH)
+    return True
+
+
+CPP_BINDING = _load_cpp_binding()
+
+if not CPP_BINDING:
+    torch.library.define(
+        "yamoe_b200::experts",
+        "(Tensor hidden_states, Tensor router_indices, Tensor routing_weights, Tensor gate_up_proj, "
+        "Tensor gate_up_proj_bias, Tensor down_proj, Tensor down_proj_bias, int expert_capacity, "
+        "int num_experts, int top_k) -> Tensor")
+    torch.library.define(
+        "yamoe_b200::experts_backward",
+        "(Tensor grad_out, Tensor hidden_states, Tensor router_indices, Tensor routing_weights, "
+        "Tensor gate_up_proj, Tensor gate_up_proj_bias, Tensor down_proj, Tensor down_proj_bias, "
+        "int expert_capacity, int num_experts, int top_k) -> Tensor[]")
 torch.library.define("yamoe_b200::sort", "(Tensor x, int end_bit, Tensor(a!) x_out, Tensor(b!) iota_out) -> ()")
 torch.library.define("yamoe_b200::batch_mm",
                      "(Tensor x, Tensor weights, Tensor batch_sizes, Tensor(a!) output, bool trans_b=False) -> Tensor")
@@ -90,7 +110,14 @@ def _validate(hidden_states, router_indices, routing_weights, gate_up_proj, gate
     return T, H, E, K
 
 
-@torch.library.impl("yamoe_b200::experts", "CUDA")
+def _impl_unless_cpp(name):
+    """Registers the Python implementation of an operator unless the C++ binding already has one."""
+    def deco(fn):
+        return fn if CPP_BINDING else torch.library.impl(name, "CUDA")(fn)
+    return deco
+
+
+@_impl_unless_cpp("yamoe_b200::experts")
 def _experts_cuda(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias, down_proj,
                   down_proj_bias, expert_capacity, num_experts, top_k):
     T, H, E, K = _validate(hidden_states, router_indices, routing_weights, gate_up_proj, gate_up_proj_bias,
@@ -115,7 +142,7 @@ def _experts_cuda(hidden_states, router_indices, routing_weights, gate_up_proj, 
     return out
 
 
-@torch.library.impl("yamoe_b200::experts_backward", "CUDA")
+@_impl_unless_cpp("yamoe_b200::experts_backward")
 def _experts_backward_cuda(grad_out, hidden_states, router_indices, routing_weights, gate_up_proj,
                            gate_up_proj_bias, down_proj, down_proj_bias, expert_capacity, num_experts, top_k):
     _require(grad_out.is_cuda, "grad_out must be CUDA")
