@@ -22,14 +22,24 @@
 // epoch number (a device counter in the rank's private state, incremented by the first kernel of
 // the call).  Flags carry the epoch of the phase that completed:
 //
-//   ep_publish_kernel     my per-expert counts -> counts[epoch & 1][rank][:] of every peer, then
-//                         flag_counts[rank] = epoch there
+//   ep_publish_kernel     clears my arrival counters, then my per-expert counts ->
+//                         counts[epoch & 1][rank][:] of every peer and flag_counts[rank] = epoch there
 //   ep_dispatch_kernel    waits until flag_counts[s] >= epoch for every source s (bounded), derives
-//                         every offset from the [G, E] counts, stores my
-//                         rows into the owners' receive buffers, and its last CTA sets
+//                         every offset from the [G, E] counts, writes this rank's tile and row
+//                         tables (state[prep] counts the CTAs that are done with them), stores my
+//                         rows into the owners' receive buffers -- after each row arrived[le] += 1
+//                         on the owner, with release semantics -- and its last CTA sets
 //                         flag_dispatch[rank] = epoch on every peer
-//   ep_wait_kernel        one warp; waits for flag_dispatch[s] >= epoch from every source (bounded)
-//   (grouped GEMMs; the last one returns result rows to their sources from its epilogue)
+//   gate_up GEMM          forward: launched with programmatic dependent launch, so it runs NEXT TO
+//                         the dispatch kernel; it starts once state[prep] is complete and loads the
+//                         rows of local expert le once arrived[le] has reached that expert's row
+//                         count (both waits bounded).  Rows travel local-expert-index major, so
+//                         expert 0 of every owner completes first: the transfer of the later
+//                         experts overlaps the tensor-core work on the earlier ones.
+//   ep_wait_kernel        backward (three row streams, no overlap): one warp waits for
+//                         flag_dispatch[s] >= epoch from every source (bounded)
+//   (further grouped GEMMs; the last one returns result rows to their sources from its epilogue,
+//   in 128-byte pieces)
 //   ep_signal_kernel      flag_return[rank] = epoch on every peer
 //   ep_combine_kernel     waits for flag_return[o] >= epoch from every owner (bounded), then sums
 //                         each token's K returned rows
@@ -58,31 +68,6 @@ struct EpTables {
   int32_t* seg_row;        // [G*per]  first local row of the rows source s sent for local expert le
   int64_t* row_dest;       // [max_rows] address of the row's slot in its source rank's back buffer, 0 for padding
 };
-
-// row_token[r] = r for kept rows, -1 for padding and for rows beyond the capacity; weight 1;
-// row_dest[r] = where the row's result goes in the peer memory of the rank it came from.
-__global__ void ep_rowtables_kernel(EpTables t, int64_t capacity, int64_t max_rows, void* const* peer_back,
-                                    int G, int per, int64_t row_bytes) {
-  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= max_rows) return;
-  int32_t tok = -1;
-  int64_t dest = 0;
-  if (r < t.rt.header[kHdrRowsUsed]) {
-    const int le = t.rt.tile_expert[r / kTileM];
-    const int64_t i = r - t.rt.pad_off[le];
-    const int64_t c = t.rt.counts[le];
-    if (i < (c < capacity ? c : capacity)) tok = (int32_t)r;
-    if (i < c && peer_back != nullptr) {
-      int s = 0;
-      while (s + 1 < G && t.seg_row[(s + 1) * per + le] <= r) ++s;
-      const int64_t dst_row = (int64_t)t.src_start[s * per + le] + (r - t.seg_row[s * per + le]);
-      dest = reinterpret_cast<int64_t>(peer_back[s]) + dst_row * row_bytes;
-    }
-  }
-  t.rt.row_token[r] = tok;
-  t.rt.row_weight[r] = 1.0f;
-  t.row_dest[r] = dest;
-}
 
 // Down-projection epilogue fused with the combine exchange: the bias-added result row goes
 // straight into the back buffer of the rank that owns the token (a peer store over NVLink);
@@ -169,11 +154,15 @@ struct EpCtrlLayout {
   __host__ __device__ int flag_counts() const { return 2 * G * E; }
   __host__ __device__ int flag_dispatch() const { return 2 * G * E + 64 * ((G + 63) / 64); }
   __host__ __device__ int flag_return() const { return 2 * G * E + 2 * 64 * ((G + 63) / 64); }
-  __host__ __device__ int words() const { return 2 * G * E + 3 * 64 * ((G + 63) / 64); }
+  // arrived[le]: rows of local expert le that have landed in this rank's receive buffer in the
+  // current call (every source adds 1 per row, with release semantics, after storing the row)
+  __host__ __device__ int arrived() const { return 2 * G * E + 3 * 64 * ((G + 63) / 64); }
+  __host__ __device__ int words() const { return arrived() + E; }
 };
 
 // Private per-rank state that lives across calls (zeroed once by the owner).
-enum EpStateSlot { kEpStateEpoch = 0, kEpStateTicket = 1 };
+//   prep: CTAs of the dispatch kernel that have finished this rank's tile and row tables
+enum EpStateSlot { kEpStateEpoch = 0, kEpStateTicket = 1, kEpStatePrep = 2 };
 
 __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
   int32_t v;
@@ -208,7 +197,12 @@ ep_publish_kernel(const int32_t* __restrict__ counts, int32_t* __restrict__ stat
     s_epoch = state[kEpStateEpoch] + 1;
     state[kEpStateEpoch] = s_epoch;
     state[kEpStateTicket] = 0;
+    state[kEpStatePrep] = 0;
   }
+  // my arrival counters start the call at zero; no peer adds to them before it has seen the count
+  // flag this kernel sets at its end
+  for (int i = threadIdx.x; i < lay.E; i += blockDim.x)
+    reinterpret_cast<int32_t*>(peer_ctrl[rank])[lay.arrived() + i] = 0;
   __syncthreads();
   const int32_t epoch = s_epoch;
   for (int i = threadIdx.x; i < lay.G * lay.E; i += blockDim.x) {
@@ -232,23 +226,55 @@ struct EpDispatchArgs {
   void* const* peer_x;           // [G] receive buffers for token rows
   void* const* peer_g;           // [G] receive buffers for gradient rows, or null
   void* const* peer_w;           // [G] receive buffers for routing weights, or null
+  void* const* peer_back;        // [G] buffers the result rows return to (for row_dest)
   void* const* peer_ctrl;        // [G]
   const int32_t* ctrl;           // this rank's control block
   int32_t* state;
-  int64_t max_rows;
+  int64_t max_rows, capacity, row_bytes;
   int S, H, E, G, rank, K;
+  int signal_rows;               // add 1 to the owner's arrived[le] after every row (forward: the GEMM waits per expert)
   uint64_t wait_ns;
 };
 
-// Persistent grid.  Shared memory: 3*E + 2 int32.
+__device__ __forceinline__ void red_release_sys_add(int32_t* p, int32_t v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// One warp copies a row of nvec 16-byte pieces, four loads in flight per lane.
+__device__ __forceinline__ void ep_copy_row(const uint4* __restrict__ s, uint4* __restrict__ d, int nvec, int lane) {
+  int v = lane;
+  for (; v + 96 < nvec; v += 128) {
+    const uint4 q0 = __ldg(s + v), q1 = __ldg(s + v + 32), q2 = __ldg(s + v + 64), q3 = __ldg(s + v + 96);
+    d[v] = q0; d[v + 32] = q1; d[v + 64] = q2; d[v + 96] = q3;
+  }
+  for (; v < nvec; v += 32) d[v] = __ldg(s + v);
+}
+
+// Persistent grid, two CTAs per SM next to a GEMM CTA (64 registers per thread), four without one.
+// Shared memory: 6*E + 2 int32.  Order of work in every CTA:
+//   1. wait for every source's counts; derive the offsets (all CTAs, in shared memory)
+//   2. this rank's tile tables (CTA 0) and its share of the row tables; state[prep] += 1
+//   3. its share of this rank's rows -> their owners, local-expert index major: first the rows of
+//      every owner's local expert 0, then of every owner's local expert 1, ...; inside one local
+//      expert index the owners are visited starting behind this rank, so that at any moment every
+//      owner receives from a different source.  An owner's experts therefore become complete in
+//      the order in which its grouped GEMM works on them.
+//   4. ticket; the last CTA sets flag_dispatch[rank] on every peer
 template <typename T>
-__global__ void __launch_bounds__(kRowWarps * 32)
+__global__ void __launch_bounds__(kRowWarps * 32, 4)
 ep_dispatch_fused_kernel(const EpDispatchArgs a, EpTables t) {
   extern __shared__ int32_t sm[];
   int32_t* tot = sm;               // [E] rows of expert e over all sources
   int32_t* before = sm + a.E;      // [E] rows of expert e from sources s < rank
   int32_t* poff = sm + 2 * a.E;    // [E] padded row offset of e inside its owner
+  int32_t* sstart = sm + 3 * a.E;  // [G*per] start of expert (rank*per+le) in source s's sorted order
+  int32_t* segr = sm + 4 * a.E;    // [G*per] first local row of the rows source s sent for local expert le
+  int32_t* xstart = sm + 5 * a.E;  // [E+1] start of every expert's rows in this rank's transfer order
   __shared__ int s_bad, s_last;
+  pdl_trigger();                   // a dependent GEMM may become resident; it gates itself on state[prep] and arrived[]
+#ifdef YB_PROF
+  if (threadIdx.x == 0) atomicMin(&g_prof[10], (unsigned long long)ep_timer_ns());
+#endif
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int E = a.E, G = a.G, per = E / G, rank = a.rank;
   const EpCtrlLayout lay{G, E};
@@ -282,6 +308,49 @@ ep_dispatch_fused_kernel(const EpDispatchArgs a, EpTables t) {
         if (rows > a.max_rows) { s_bad = kStatusEpOverflow; break; }
       }
     }
+    // way back: where source s keeps the rows of my local expert le in its sorted order
+    for (int s = tid; s < G; s += nthr) {
+      int run = 0;
+      for (int e = 0; e < (rank + 1) * per; ++e) {
+        if (e >= rank * per) sstart[s * per + (e - rank * per)] = run;
+        run += max(__ldcg(counts_all + s * E + e), 0);
+      }
+    }
+    // my transfer order: position x = le * G + ((owner - rank - 1) mod G); exclusive scan of the
+    // row counts in that order by warp 0 (each lane a run of consecutive positions).  The counts
+    // sit in segr for the moment (it gets its own contents below).
+    for (int x = tid; x < E; x += nthr) {
+      const int le = x / G, owner = (rank + 1 + (x - le * G)) % G;
+      const int e = owner * per + le;
+      segr[x] = a.bins[e] - (e ? a.bins[e - 1] : 0);
+    }
+    __syncthreads();
+    if (tid < 32) {
+      const int chunk = (E + 31) / 32, x0 = min(tid * chunk, E), x1 = min(x0 + chunk, E);
+      int sum = 0;
+      for (int x = x0; x < x1; ++x) sum += segr[x];
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (tid >= o) incl += v;
+      }
+      int run = incl - sum;
+      for (int x = x0; x < x1; ++x) {
+        xstart[x] = run;
+        run += segr[x];
+      }
+      if (tid == 31) xstart[E] = incl;
+    }
+    __syncthreads();
+    // first local row of the rows source s sent for my local expert le
+    for (int le = tid; le < per; le += nthr) {
+      int row = poff[rank * per + le];
+      for (int s = 0; s < G; ++s) {
+        segr[s * per + le] = row;
+        row += max(__ldcg(counts_all + s * E + rank * per + le), 0);
+      }
+    }
     __syncthreads();
   }
   const int bad = s_bad;
@@ -303,13 +372,8 @@ ep_dispatch_fused_kernel(const EpDispatchArgs a, EpTables t) {
       }
     } else {
       for (int i = tid; i < G * per; i += nthr) {
-        const int s = i / per, le = i - s * per, e = rank * per + le;
-        int start = 0;
-        for (int e2 = 0; e2 < e; ++e2) start += max(__ldcg(counts_all + s * E + e2), 0);
-        int row = poff[e];
-        for (int s2 = 0; s2 < s; ++s2) row += max(__ldcg(counts_all + s2 * E + e), 0);
-        t.src_start[i] = start;
-        t.seg_row[i] = row;
+        t.src_start[i] = sstart[i];
+        t.seg_row[i] = segr[i];
       }
       if (tid == 0) {
         int rows = 0, pairs = 0, cum = 0;
@@ -336,42 +400,104 @@ ep_dispatch_fused_kernel(const EpDispatchArgs a, EpTables t) {
       }
     }
   }
+  // ---- this CTA's share of the row tables: validity of every local row and where its result goes --
+  // row_token[r] = r for kept rows, -1 for padding and for rows beyond the capacity; weight 1;
+  // row_dest[r] = the row's slot in the back buffer of the rank it came from, 0 for padding.
+  {
+    const int me = rank * per;
+    const int used = bad ? 0 : poff[me + per - 1] + (tot[me + per - 1] + kTileM - 1) / kTileM * kTileM;
+    const int64_t chunk = (a.max_rows + gridDim.x - 1) / gridDim.x;
+    const int64_t r_end = min((int64_t)(blockIdx.x + 1) * chunk, a.max_rows);
+    for (int64_t r = (int64_t)blockIdx.x * chunk + tid; r < r_end; r += nthr) {
+      int32_t tok = -1;
+      int64_t dest = 0;
+      if (r < used) {
+        int lo = 0, hi = per - 1;                      // last local expert whose first row is <= r
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (poff[me + mid] <= r) lo = mid; else hi = mid - 1;
+        }
+        const int le = lo;
+        const int64_t i = r - poff[me + le];
+        const int64_t c = tot[me + le];
+        if (i < (c < a.capacity ? c : a.capacity)) tok = (int32_t)r;
+        if (i < c && a.peer_back != nullptr) {
+          int sidx = 0;
+          while (sidx + 1 < G && segr[(sidx + 1) * per + le] <= r) ++sidx;
+          const int64_t dst_row = (int64_t)sstart[sidx * per + le] + (r - segr[sidx * per + le]);
+          dest = reinterpret_cast<int64_t>(a.peer_back[sidx]) + dst_row * a.row_bytes;
+        }
+      }
+      t.rt.row_token[r] = tok;
+      t.rt.row_weight[r] = 1.0f;
+      t.row_dest[r] = dest;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) atomicAdd(a.state + kEpStatePrep, 1);
+  }
   // ---- my rows -> their owners -------------------------------------------------------------------
   if (bad == 0) {
     const int warp = tid >> 5, lane = tid & 31;
-    const int n_valid = a.bins[E - 1];
-    // start with the rows of the next rank's experts, so that the G sources do not all begin with
-    // owner 0: at any moment every owner receives from a different source
-    const int first_e = ((rank + 1) % G) * per;
-    const int rot = first_e ? a.bins[first_e - 1] : 0;
     const int nvec = a.H * (int)sizeof(T) / 16;
-    for (int jj = blockIdx.x * kRowWarps + warp; jj < n_valid; jj += gridDim.x * kRowWarps) {
-      int j = jj + rot;
-      if (j >= n_valid) j -= n_valid;
-      const int e = a.sorted_values[j];
-      const int i = j - (e ? a.bins[e - 1] : 0);
-      const int flat = a.sorted_indices[j];
-      const int tok = flat / a.K;
-      const int owner = e / per;
-      const int64_t drow = (int64_t)poff[e] + before[e] + i;
-      if (drow >= a.max_rows) continue;          // cannot happen once the totals passed the check
-      {
-        const uint4* s = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.hidden) + (size_t)tok * a.H);
-        uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.peer_x[owner]) + (size_t)drow * a.H);
-        for (int v = lane; v < nvec; v += 32) d[v] = __ldg(s + v);
+    // A warp takes four consecutive transfer positions per trip: their stores are in flight
+    // together, and rows of the same expert share one release.
+    constexpr int kRowsPerTrip = 4;
+    // Phase le = the rows of every owner's local expert le.  The phases are walked in order by all
+    // warps, so the rows of phase le are (nearly) all on their way before those of phase le + 1
+    // start: experts complete at their owners in the order the owners' GEMMs want them.  The warp
+    // that takes the first rows of a phase rotates, so that small phases do not all land on the
+    // same few SMs.
+    const int nw = gridDim.x * kRowWarps, gw = blockIdx.x * kRowWarps + warp;
+    for (int ph = 0; ph < per; ++ph) {
+    const int p0 = xstart[ph * G], p1 = xstart[(ph + 1) * G];
+    const int slot = (gw + ph * 251) % nw;
+    for (int base = p0 + slot * kRowsPerTrip; base < p1; base += nw * kRowsPerTrip) {
+      int sig_owner = -1, sig_le = 0, sig_n = 0;       // rows stored but not yet announced
+      for (int jj = base; jj < min(base + kRowsPerTrip, p1); ++jj) {
+        int lo = 0, hi = E - 1;                        // transfer position x with xstart[x] <= jj < xstart[x+1]
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (xstart[mid] <= jj) lo = mid; else hi = mid - 1;
+        }
+        const int le = lo / G, owner = (rank + 1 + (lo - le * G)) % G;
+        const int e = owner * per + le;
+        const int i = jj - xstart[lo];
+        const int j = (e ? a.bins[e - 1] : 0) + i;     // position in my sorted order
+        const int flat = a.sorted_indices[j];
+        const int tok = flat / a.K;
+        const int64_t drow = (int64_t)poff[e] + before[e] + i;
+        if (drow >= a.max_rows) continue;        // cannot happen once the totals passed the check
+        if (a.signal_rows && sig_n > 0 && (owner != sig_owner || le != sig_le)) {
+          __syncwarp();
+          if (lane == 0)
+            red_release_sys_add(reinterpret_cast<int32_t*>(a.peer_ctrl[sig_owner]) + lay.arrived() + sig_le, sig_n);
+          sig_n = 0;
+        }
+        ep_copy_row(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.hidden) + (size_t)tok * a.H),
+                    reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.peer_x[owner]) + (size_t)drow * a.H), nvec, lane);
+        if (a.grad != nullptr)
+          ep_copy_row(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.grad) + (size_t)tok * a.H),
+                      reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.peer_g[owner]) + (size_t)drow * a.H), nvec, lane);
+        if (a.routing_weights != nullptr && lane == 0) {
+          const size_t idx = a.routing_cols == E ? (size_t)tok * E + e : (size_t)flat;
+          reinterpret_cast<float*>(a.peer_w[owner])[drow] =
+              DT<T>::ld(reinterpret_cast<const T*>(a.routing_weights) + idx);
+        }
+        sig_owner = owner; sig_le = le; ++sig_n;
       }
-      if (a.grad != nullptr) {
-        const uint4* s = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.grad) + (size_t)tok * a.H);
-        uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.peer_g[owner]) + (size_t)drow * a.H);
-        for (int v = lane; v < nvec; v += 32) d[v] = __ldg(s + v);
-      }
-      if (a.routing_weights != nullptr && lane == 0) {
-        const size_t idx = a.routing_cols == E ? (size_t)tok * E + e : (size_t)flat;
-        reinterpret_cast<float*>(a.peer_w[owner])[drow] =
-            DT<T>::ld(reinterpret_cast<const T*>(a.routing_weights) + idx);
+      if (a.signal_rows && sig_n > 0) {
+        // the rows are complete once every lane's stores are ordered before lane 0's release
+        __syncwarp();
+        if (lane == 0)
+          red_release_sys_add(reinterpret_cast<int32_t*>(a.peer_ctrl[sig_owner]) + lay.arrived() + sig_le, sig_n);
       }
     }
+    }
   }
+#ifdef YB_PROF
+  if (threadIdx.x == 0) atomicMax(&g_prof[11], (unsigned long long)ep_timer_ns());
+#endif
   // ---- the last CTA tells every owner that this rank's rows are in place -----------------------
   __threadfence_system();
   __syncthreads();

@@ -247,12 +247,21 @@ struct EpiScatterAdd {
 // pre-activations, scaled by the routing weight, to g_pre[row, 2*j0 .. 2*j0+2NV).
 template <typename T>
 struct EpiGluBackward {
+  static constexpr bool kPrefetchTile = true;
   const T* pre;              // [rows, 2H] biased pre-activations from the recompute
   T* g_pre;                  // [rows, 2H]
   float* gw_row;             // [rows]
   const int32_t* row_token;
   const float* row_weight;
   int H;
+
+  // the 2*ncols pre-activations this row's epilogue will read for output columns n0 .. n0+ncols
+  __device__ __forceinline__ void prefetch_tile(int row, int n0, int ncols) const {
+    if (row_token[row] < 0) return;
+    const char* p = reinterpret_cast<const char*>(pre + (size_t)row * 2 * H + 2 * n0);
+    for (int b = 0; b < 2 * ncols * (int)sizeof(T); b += 128)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p + b));
+  }
 
   template <int NV>
   __device__ __forceinline__ void apply(int /*e*/, int row, int n0, const float (&v)[NV]) const {

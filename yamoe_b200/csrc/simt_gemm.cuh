@@ -17,6 +17,18 @@ namespace yb {
 
 enum GemmMode { kFwd = 0, kDgrad = 1, kWgrad = 2 };
 
+// Optional gate of a row-tiled tcgen05 GEMM that is launched while the kernel that fills its A rows
+// is still running (programmatic dependent launch): the kernel starts only once *prep has reached
+// prep_target (tables complete), and loads the A rows of group e only once arrived[e] >= needed[e].
+// Both waits poll local memory, are bounded by wait_ns and record a device status when they give up.
+struct GemmGate {
+  const int32_t* prep = nullptr;
+  int prep_target = 0;
+  const int32_t* arrived = nullptr;
+  const int32_t* needed = nullptr;
+  unsigned long long wait_ns = 0;
+};
+
 struct GemmArgs {
   const void* A; int64_t lda;
   const void* B; int64_t ldb; int64_t b_expert_stride;
@@ -29,7 +41,7 @@ struct GemmArgs {
   const int32_t* header;
   const int32_t* pair_expert = nullptr;   // tile-pair tables (256-row tcgen05 kernel only)
   const int32_t* pair_off = nullptr;
-  const int32_t* counts = nullptr;        // rows present per expert (swapped-operand tcgen05 kernel only)
+  const int32_t* counts = nullptr;        // rows present per expert: lets the CUDA-core kernel skip all-padding tiles
   // tcgen05 kFwd only: A is the UN-permuted source [gather_src_rows, K]; row r of the padded layout
   // is source row gather_rows[r] (negative = padding), fetched by TMA gather
   const int32_t* gather_rows = nullptr;
@@ -37,6 +49,7 @@ struct GemmArgs {
   // row-tiled arrangements without tables (tile_expert == nullptr): one group (expert 0) owns the
   // a_rows rows of A; rows at and beyond a_rows read as zeros
   int64_t a_rows = 0;
+  GemmGate gate;                          // tcgen05 kFwd only
 };
 
 constexpr int kSimtBN = 128, kSimtBK = 16, kSimtThreads = 256;

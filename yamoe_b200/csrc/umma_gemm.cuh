@@ -27,6 +27,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -55,7 +56,8 @@ __device__ unsigned long long g_prof[16];
 #define YB_PROF_FLUSH(slot, var)
 #endif
 
-enum DeviceStatus { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusMmaTimeout = 2, kStatusEpilogueTimeout = 3 };
+enum DeviceStatus { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusMmaTimeout = 2, kStatusEpilogueTimeout = 3,
+                    kStatusGateTimeout = 5 };   // 5: rows that another GPU was to deliver did not arrive in time
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -193,6 +195,15 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
 //   kOutPerChunk                                    32, or 16 for a functor that turns column pairs into one value
 //   T* row_ptr(int row) const                       start of the output row, or nullptr to skip it
 //   values<32>(e, row, n0, v, o) const              o[0 .. kOutPerChunk) = the outputs of accumulator columns n0 .. n0+31
+// Functors that read a tile-shaped operand of their own in the epilogue (EpiGluBackward reads the
+// stored pre-activations) may declare `prefetch_tile(row, n0, ncols)`: the epilogue calls it for
+// its row before it waits for the accumulator, so that those lines are on their way to L2/L1
+// while the main loop of the tile is still running.
+template <class E, class = void>
+struct epi_prefetches : std::false_type {};
+template <class E>
+struct epi_prefetches<E, std::enable_if_t<E::kPrefetchTile>> : std::true_type {};
+
 template <class E, class = void>
 struct epi_staged : std::false_type {};
 template <class E>
@@ -206,6 +217,7 @@ struct UmmaParams {
   int uniform_tiles;
   int32_t* header;
   const int32_t* gather_rows;   // kFwd: source row of every padded row (TMA gather of A), or null
+  GemmGate gate;                // see GemmGate
 };
 
 template <int BN>
@@ -261,7 +273,32 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // Set-up is done: let the next kernel on the stream begin its own set-up, then wait until the
   // previous kernel has completed before touching anything it produced.
   pdl_trigger();
-  pdl_wait();
+  const bool gated = p.gate.prep != nullptr;
+#ifdef YB_PROF
+  if (gated && threadIdx.x == 0) atomicMin(&g_prof[8], (unsigned long long)global_timer_ns());
+#endif
+  if (!gated) {
+    pdl_wait();
+  } else {
+    // launched next to the kernel that fills the tables and the A rows: no wait for its completion,
+    // only for the tables (bounded); a time-out leaves this kernel without work
+    if (threadIdx.x == 0) {
+      const uint64_t t0 = global_timer_ns();
+      int ready = 1;
+      for (;;) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.gate.prep) : "memory");
+        if (v >= p.gate.prep_target) break;
+        if (global_timer_ns() - t0 > p.gate.wait_ns) { ready = 0; break; }
+        __nanosleep(200);
+      }
+      if (!ready) {
+        abort_flag = 1;
+        atomicMax(p.header + kHdrStatus, (int)kStatusGateTimeout);
+      }
+    }
+    __syncthreads();
+  }
   const bool uniform = p.tile_expert == nullptr && MODE != kWgrad;
   const bool pad_in_smem = uniform || p.E <= kUmmaMaxExperts;
   if (pad_in_smem) {
@@ -284,6 +321,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     total = (uniform ? p.uniform_tiles : p.header[kHdrRowTiles]) * NT;
   }
+  if (gated && abort_flag != 0) total = 0;
   // Expert of tile `id` for the row-tiled arrangements: the only part of a tile's description
   // that comes from global memory.  Every role asks for it one tile ahead.
   auto expert_of = [&](int id) -> int {
@@ -363,6 +401,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       long long prof_empty = 0;
       (void)prof_empty;
+      int gate_done = -1;                  // last group whose rows are known to have arrived
       int e_next = expert_of(blockIdx.x);
       for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
         int e, row0, n0, krow, kblocks;
@@ -372,6 +411,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // (The K-major B of the data gradients is one box of BN rows; rows past N read as zeros.)
         const int nboxes = MODE == kDgrad ? BN / 64 : (min(BN, p.N - n0) + 63) >> 6;
         const uint32_t stage_tx = SM::kABytes + nboxes * 8192;
+        if (MODE == kFwd && p.gate.arrived != nullptr && e != gate_done) {
+          // the A rows of this group come from other GPUs: all of them must have landed
+          const int need = p.gate.needed[e];
+          const uint64_t t0 = global_timer_ns();
+          for (;;) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.gate.arrived + e) : "memory");
+            if (v >= need) break;
+            if (abort_flag != 0 || global_timer_ns() - t0 > p.gate.wait_ns) { ok = false; break; }
+            __nanosleep(100);
+          }
+          if (!ok) {
+            abort_flag = 1;
+            atomicMax(p.header + kHdrStatus, (int)kStatusGateTimeout);
+            break;
+          }
+          asm volatile("fence.proxy.async.global;" ::: "memory");   // the TMA loads below read what those stores wrote
+#ifdef YB_PROF
+          if (gate_done < 0) atomicMax(&g_prof[9], (unsigned long long)global_timer_ns());
+          atomicMax(&g_prof[12], (unsigned long long)global_timer_ns());
+#endif
+          gate_done = e;
+        }
         for (int kb = 0; kb < kblocks; ++kb) {
           YB_PROF_T0
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
@@ -501,6 +563,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (n0 + c * 32 < p.N) epi.template apply<32>(e, row, n0 + c * 32, z);
         continue;
       }
+      if constexpr (epi_prefetches<Epi>::value) epi.prefetch_tile(row, n0, min(BN, p.N - n0));
       if (!mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, &abort_flag)) {
         abort_flag = 1;
         atomicMax(p.header + kHdrStatus, (int)kStatusEpilogueTimeout);
@@ -626,8 +689,41 @@ inline EncodeTiledFn encode_tiled_fn() {
 inline bool umma_available() { return encode_tiled_fn() != nullptr; }
 
 // bf16 tensor map with 128-byte swizzle; dims / box innermost first, strides in bytes for dims 1...
+// Encoding a map is a driver call that costs some tens of microseconds of host time; the same
+// (pointer, shape, box) comes back call after call (weights, persistent buffers, workspaces that the
+// caching allocator hands out again), so the last maps are kept in a small table.
+struct TensorMapKey {
+  const void* base;
+  int rank;
+  uint64_t dims[3], strides[2];
+  uint32_t box[3];
+  bool operator==(const TensorMapKey& o) const {
+    if (base != o.base || rank != o.rank) return false;
+    for (int i = 0; i < rank; ++i)
+      if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
+    for (int i = 0; i + 1 < rank; ++i)
+      if (strides[i] != o.strides[i]) return false;
+    return true;
+  }
+};
+
 inline bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
                      const uint32_t* box) {
+  constexpr int kSlots = 32;
+  static TensorMapKey keys[kSlots];
+  static CUtensorMap maps[kSlots];
+  static int used = 0, next = 0;
+  static std::mutex mu;
+  TensorMapKey key{};
+  key.base = base;
+  key.rank = rank;
+  for (int i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides[i];
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; ++i)
+      if (keys[i] == key) { *m = maps[i]; return true; }
+  }
   cuuint64_t gd[3];
   cuuint64_t gs[2];
   cuuint32_t bx[3], es[3] = {1, 1, 1};
@@ -636,7 +732,12 @@ inline bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t*
   CUresult r = encode_tiled_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gd,
                                  gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  const int slot = used < kSlots ? used++ : (next = (next + 1) % kSlots);
+  keys[slot] = key;
+  maps[slot] = *m;
+  return true;
 }
 
 inline int umma_sm_count() {
@@ -699,12 +800,14 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
     attr_done = true;
   }
   UmmaParams p{g.M, g.N, g.K, g.E, g.tile_expert, g.pad_off, (int)max_tiles, const_cast<int32_t*>(g.header),
-               MODE == kFwd ? g.gather_rows : nullptr};
+               MODE == kFwd ? g.gather_rows : nullptr, g.gate};
   const int NT = (int)ceil_div(g.N, BN);
   int64_t total_max = MODE == kWgrad ? (int64_t)g.E * ceil_div(g.M, kUmmaBM) * NT : max_tiles * NT;
   int grid = (int)std::min<int64_t>(total_max, umma_sm_count());
   if (grid <= 0) return YAMOE_OK;
-  if (launch_pdl(kern, dim3(grid), dim3(kUmmaThreads), SM::kTotal, stream, tmA, tmB, p, epi) != cudaSuccess)
+  // a gated GEMM is meant to start while its predecessor on the stream still runs
+  if (launch_pdl_opt(g.gate.prep != nullptr, kern, dim3(grid), dim3(kUmmaThreads), SM::kTotal, stream, tmA, tmB, p, epi) !=
+      cudaSuccess)
     return YAMOE_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }

@@ -163,9 +163,16 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         decode(id, e_next, e, row0, has1, n0);
         e_next = expert_of(id + n_clusters);
         const bool load_a = leader || has1;
-        const uint32_t bytes = (load_a ? kU2ABytes : 0) + kU2BBytes;
+        // The last column tile may be narrower (a multiple of 64 columns): the pair then multiplies by
+        // ncols columns and each CTA stages half of them.  MN-major B (forward) comes in 64-column
+        // boxes, so a half of 32 columns still loads one box and uses its first 32 columns; the
+        // K-major B of the data gradients is one box of 128 rows whatever the half is.
+        const int ncols = min(BN, p.N - n0);
+        const int half = ncols >> 1;
+        const int bboxes = MODE == kFwd ? (half + 63) >> 6 : 2;
+        const uint32_t bytes = (load_a ? kU2ABytes : 0) + bboxes * 8192;
         const int my_row0 = row0 + (int)rank * 128;
-        const int my_n0 = n0 + (int)rank * 128;
+        const int my_n0 = n0 + (int)rank * half;
         for (int kb = 0; kb < kblocks; ++kb) {
           YB_PROF_T0
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
@@ -187,7 +194,7 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (load_a) tma2_load_2d(sa, &tmA, kb * kUmmaBK, my_row0, full);
           if constexpr (MODE == kFwd) {
             tma2_load_3d(sb, &tmB, my_n0, kb * kUmmaBK, e, full);
-            tma2_load_3d(sb + 8192, &tmB, my_n0 + 64, kb * kUmmaBK, e, full);
+            if (bboxes > 1) tma2_load_3d(sb + 8192, &tmB, my_n0 + 64, kb * kUmmaBK, e, full);
           } else {
             tma2_load_3d(sb, &tmB, kb * kUmmaBK, my_n0, e, full);
           }
@@ -201,8 +208,9 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     // =========================== MMA issuer (leader CTA only) ================================
     if (leader && lane == 0) {
       constexpr bool kBMn = (MODE == kFwd);
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kBMn ? 1u : 0u) << 16) |
-                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+      // instruction descriptor without its N field (bits 17..22 = N / 8), which depends on the tile
+      constexpr uint32_t idesc_base = (1u << 4) | (1u << 7) | (1u << 10) | ((kBMn ? 1u : 0u) << 16) |
+                                      ((uint32_t)(256 >> 4) << 24);
       constexpr uint32_t a_kstep = 32 >> 4;
       constexpr uint32_t b_kstep = kBMn ? (16 * 128) >> 4 : 32 >> 4;
       int stage = 0, acc = 0;
@@ -213,7 +221,13 @@ umma_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #ifdef YB_PROF
       const long long prof_begin = clock64();
 #endif
+      int e_next = expert_of(cluster_id);
       for (int id = cluster_id; id < total && ok; id += n_clusters) {
+        int e, row0, n0;
+        bool has1;
+        decode(id, e_next, e, row0, has1, n0);
+        e_next = expert_of(id + n_clusters);
+        const uint32_t idesc = idesc_base | ((uint32_t)(min(BN, p.N - n0) >> 3) << 17);
         {
           YB_PROF_T0
           if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, &abort_flag)) { ok = false; break; }
@@ -369,6 +383,16 @@ inline int launch_umma_gemm_2cta(const GemmArgs& g, const Epi& epi, int64_t max_
   if (grid <= 0) return YAMOE_OK;
   kern<<<grid, kU2Threads, kU2Smem, stream>>>(tmA, tmB, p, epi);
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
+}
+
+// Row-tiled GEMMs: pair kernel (when selected and the tile-pair tables exist) or one-CTA kernel.
+template <int MODE, class Epi>
+inline int launch_umma(const GemmArgs& g, const Epi& epi, int64_t max_rows, int64_t max_tiles, cudaStream_t stream) {
+  if constexpr (MODE != kWgrad) {
+    const bool pairs = g.pair_expert != nullptr && g.pair_off != nullptr && g.gather_rows == nullptr;
+    if (pairs && umma_2cta_enabled()) return launch_umma_gemm_2cta<MODE>(g, epi, max_rows, max_tiles, stream);
+  }
+  return launch_umma_gemm<MODE>(g, epi, max_rows, max_tiles, stream);
 }
 
 }  // namespace yb

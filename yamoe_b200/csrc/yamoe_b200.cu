@@ -17,7 +17,6 @@
 #include "simt_gemm.cuh"
 #include "umma_gemm.cuh"
 #include "umma_gemm_2cta.cuh"
-#include "umma_gemm_swap.cuh"
 #include "gemv.cuh"
 #include "ep_fused.cuh"
 #include "router.cuh"
@@ -504,7 +503,7 @@ static int check_ep(int64_t max_rows, int H, int E, int G, int rank, int dtype) 
 template <typename T>
 static int ep_local_forward_impl(const void* recv_x, const void* wgu, const void* bgu, const void* wd,
                                  const void* bd, void* yrows, int64_t max_rows, int H, int per, int dtype,
-                                 const EpPlan& p, cudaStream_t st) {
+                                 const EpPlan& p, cudaStream_t st, const GemmGate& gate = GemmGate{}) {
   const RouteTables& rt = p.t.rt;
   const int64_t max_tiles = max_rows / kTileM;
   EpiGluAct<T> glu{reinterpret_cast<const T*>(bgu), reinterpret_cast<T*>(p.act), rt.row_token, H};
@@ -515,6 +514,7 @@ static int ep_local_forward_impl(const void* recv_x, const void* wgu, const void
   GemmArgs g1{recv_x, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, per, rt.tile_expert, rt.pad_off,
               rt.header};
   g1.pair_expert = rt.pair_expert; g1.pair_off = rt.pair_off; g1.counts = rt.counts;
+  g1.gate = gate;
   GemmArgs g2{p.act, H, wd, H, (int64_t)H * H, 0, H, H, per, rt.tile_expert, rt.pad_off, rt.header};
   g2.pair_expert = rt.pair_expert; g2.pair_off = rt.pair_off; g2.counts = rt.counts;
   int rc = YAMOE_OK;
@@ -522,7 +522,9 @@ static int ep_local_forward_impl(const void* recv_x, const void* wgu, const void
     if constexpr (sizeof(T) == 2) {
       {
         StageTimer tm(kStageGateUp, st);
-        rc = launch_umma<kFwd>(g1, glu, max_rows, max_tiles, st);
+        // the gate is a feature of the one-CTA kernel
+        rc = gate.prep != nullptr ? launch_umma_gemm<kFwd>(g1, glu, max_rows, max_tiles, st)
+                                  : launch_umma<kFwd>(g1, glu, max_rows, max_tiles, st);
       }
       if (rc) return rc;
       StageTimer tm(kStageDown, st);
@@ -638,10 +640,13 @@ static int check_ep_ctx(const yamoe_ep_ctx_t* c, bool backward) {
 
 // Steps shared by the forward and the backward call, up to the point where every row this rank's
 // experts need has arrived: local sort, count exchange, dispatch, row tables, wait.
+// With `gate` (forward on the tcgen05 path) the prologue ends with the dispatch kernel still
+// running: *gate is filled in for the gate_up GEMM, which is launched next to it and waits for each
+// expert's rows by itself.  Otherwise the prologue ends with the wait for all sources.
 template <typename T>
 static int ep_call_prologue(const yamoe_ep_ctx_t& c, const EpCallPlan& p, const void* hidden, const void* grad,
                             const int64_t* ridx, const void* rw, int rcols, int64_t Tn, int64_t cap,
-                            void* const* peer_back, cudaStream_t st) {
+                            void* const* peer_back, cudaStream_t st, GemmGate* gate = nullptr) {
   const int64_t S = Tn * c.K;
   const uint64_t wait_ns = c.wait_ns ? c.wait_ns : kWaitLimitNs;
   const EpCtrlLayout lay{c.G, c.E};
@@ -667,19 +672,42 @@ static int ep_call_prologue(const yamoe_ep_ctx_t& c, const EpCallPlan& p, const 
   a.peer_x = c.peer_recv_x;
   a.peer_g = c.peer_recv_g;
   a.peer_w = c.peer_recv_w;
+  a.peer_back = peer_back;
   a.peer_ctrl = c.peer_ctrl;
   a.ctrl = reinterpret_cast<const int32_t*>(c.ctrl);
   a.state = reinterpret_cast<int32_t*>(c.state);
   a.max_rows = c.max_rows;
+  a.capacity = cap;
+  a.row_bytes = (int64_t)c.H * sizeof(T);
   a.S = (int)S; a.H = c.H; a.E = c.E; a.G = c.G; a.rank = c.rank; a.K = c.K;
+  a.signal_rows = gate != nullptr ? 1 : 0;
   a.wait_ns = wait_ns;
-  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div(S, kRowWarps), (int64_t)umma_sm_count() * 6));
-  ep_dispatch_fused_kernel<T><<<grid, kRowWarps * 32, (size_t)(3 * c.E + 2) * sizeof(int32_t), st>>>(a, p.ep.t);
-  ep_rowtables_kernel<<<(unsigned)ceil_div(c.max_rows, 256), 256, 0, st>>>(
-      p.ep.t, cap, c.max_rows, peer_back, c.G, c.E / c.G, (int64_t)c.H * sizeof(T));
-  ep_wait_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const int32_t*>(c.ctrl) + lay.flag_dispatch(), c.G,
-                                   reinterpret_cast<const int32_t*>(c.state), p.ep.t.rt.header,
-                                   (int)kStatusEpDispatchTimeout, wait_ns);
+  // Next to a GEMM CTA an SM has registers for two of these CTAs; alone, for four.  The kernel asks
+  // for the same (maximal) shared-memory carve-out as the GEMM: CTAs of kernels with different
+  // carve-outs do not share an SM.
+  const int grid = (int)std::max<int64_t>(
+      1, std::min<int64_t>(std::max<int64_t>(ceil_div(S, kRowWarps * 4), ceil_div(c.max_rows, 4096)),
+                           (int64_t)umma_sm_count() * (gate != nullptr ? 2 : 4)));
+  {
+    static std::atomic<bool> carveout_set{false};    // per template instantiation
+    if (!carveout_set.load()) {
+      cudaFuncSetAttribute(ep_dispatch_fused_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           (int)cudaSharedmemCarveoutMaxShared);
+      carveout_set.store(true);
+    }
+  }
+  ep_dispatch_fused_kernel<T><<<grid, kRowWarps * 32, (size_t)(6 * c.E + 2) * sizeof(int32_t), st>>>(a, p.ep.t);
+  if (gate != nullptr) {
+    gate->prep = reinterpret_cast<const int32_t*>(c.state) + kEpStatePrep;
+    gate->prep_target = grid;
+    gate->arrived = reinterpret_cast<const int32_t*>(c.ctrl) + lay.arrived();
+    gate->needed = p.ep.t.rt.counts;
+    gate->wait_ns = wait_ns;
+  } else {
+    ep_wait_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const int32_t*>(c.ctrl) + lay.flag_dispatch(), c.G,
+                                     reinterpret_cast<const int32_t*>(c.state), p.ep.t.rt.header,
+                                     (int)kStatusEpDispatchTimeout, wait_ns);
+  }
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
@@ -691,14 +719,24 @@ static int ep_forward_impl(const yamoe_ep_ctx_t& c, const void* hidden, const in
   const EpCtrlLayout lay{c.G, c.E};
   const uint64_t wait_ns = c.wait_ns ? c.wait_ns : kWaitLimitNs;
   int rc;
+  // The gate_up GEMM overlaps the dispatch when it is the tcgen05 kernel; YAMOE_B200_EP_OVERLAP=0
+  // keeps the two apart (dispatch, wait for all sources, then the GEMMs).
+  static const bool overlap_env = []() {
+    const char* env = std::getenv("YAMOE_B200_EP_OVERLAP");
+    return env == nullptr || std::atoi(env) != 0;
+  }();
+  const bool overlap = overlap_env && sizeof(T) == 2 && use_tcgen05(current_path(), c.dtype, c.H);
+  GemmGate gate;
   {
     StageTimer tm(kStageEpDispatch, st);
-    rc = ep_call_prologue<T>(c, p, hidden, nullptr, ridx, rw, rcols, Tn, cap, c.peer_back, st);
+    rc = ep_call_prologue<T>(c, p, hidden, nullptr, ridx, rw, rcols, Tn, cap, c.peer_back, st,
+                             overlap ? &gate : nullptr);
   }
   if (rc) return rc;
   // gate_up + GLU + down on the received rows; the down GEMM's epilogue stores every result row
   // into the back buffer of the rank that owns the token
-  rc = ep_local_forward_impl<T>(c.recv_x, wgu, bgu, wd, bd, nullptr, c.max_rows, c.H, c.E / c.G, c.dtype, p.ep, st);
+  rc = ep_local_forward_impl<T>(c.recv_x, wgu, bgu, wd, bd, nullptr, c.max_rows, c.H, c.E / c.G, c.dtype, p.ep, st,
+                                gate);
   if (rc) return rc;
   StageTimer tm(kStageEpCombine, st);
   ep_signal_kernel<<<1, 32, 0, st>>>(c.peer_ctrl, lay.flag_return(), c.G, c.rank,
@@ -1249,6 +1287,7 @@ int yamoe_b200_index_select(void* out, const void* in, const int32_t* idx, int64
 #ifdef YB_PROF
 int yamoe_b200_prof_read(unsigned long long* out16) {
   unsigned long long zero[16] = {};
+  zero[8] = zero[10] = ~0ull;          // slots that hold a minimum
   if (cudaDeviceSynchronize() != cudaSuccess) return YAMOE_ERR_CUDA;
   if (cudaMemcpyFromSymbol(out16, g_prof, sizeof(zero)) != cudaSuccess) return YAMOE_ERR_CUDA;
   if (cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)) != cudaSuccess) return YAMOE_ERR_CUDA;

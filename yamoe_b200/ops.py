@@ -23,6 +23,8 @@ def _load_cpp_binding() -> bool:
     Python registration below (used by the tests that compare the two)."""
     if os.environ.get("YAMOE_B200_PY_BINDING", "0") not in ("", "0"):
         return False
+    if os.environ.get("YAMOE_B200_LIB"):
+        return False                 # the binding is linked against the default build of the library
     from .build import BINDING_PATH
     if not os.path.exists(BINDING_PATH):
         return False
