@@ -87,7 +87,7 @@ def measured_peaks():
 
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -103,7 +103,10 @@ class ClockSampler:
             self.proc = None
         return self
 
-    def stop(self):
+    def stop(self, window=None):
+        """Ends the sampling.  `window` = (t0, t1) in time.time() seconds keeps only the samples whose
+        own timestamp lies inside it (the sampler is started early, because nvidia-smi needs a few
+        hundred milliseconds before its first line)."""
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         self.proc.terminate()
@@ -114,10 +117,18 @@ class ClockSampler:
             out, _ = self.proc.communicate()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        import datetime
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
+            if window is not None:
+                try:
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                except ValueError:
+                    continue
+                if not (window[0] - 0.025 <= ts <= window[1] + 0.025):
+                    continue
             try:
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
@@ -447,6 +458,7 @@ def time_resident(case: Case, steps: int, warmup: int, sample_clocks: bool = Tru
     from yamoe_b200 import _lib
     env, torch = case.env, case.env.torch
     L = _lib.lib()
+    sampler = ClockSampler(env.local_rank).start() if sample_clocks else None
     for _ in range(warmup):
         case.run()
     env.sync_all()
@@ -454,9 +466,9 @@ def time_resident(case: Case, steps: int, warmup: int, sample_clocks: bool = Tru
     for a, b in pairs:
         a.record(); b.record()           # forces creation of the underlying cudaEvent_t
     torch.cuda.synchronize()
-    sampler = ClockSampler(env.local_rank).start() if sample_clocks else None
     t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     env.sync_all()
+    wall0 = time.time()
     eager_us = None
     if case.decode:
         # Touched weights (0.2 - 5.8 GB) are comparable to the 126 MB L2 at T=1: flush it between
@@ -502,9 +514,22 @@ def time_resident(case: Case, steps: int, warmup: int, sample_clocks: bool = Tru
         env.sync_all()
         ms_total = t_start.elapsed_time(t_stop)
     L.yamoe_b200_set_stage_events(None, None, 0)
-    clocks = sampler.stop() if sampler is not None else None
+    wall1 = time.time()
     gemm_ms = [a.elapsed_time(b) for a, b in pairs] if case.mode == "fwd" else []
     ms_step = env.max_over_ranks(ms_total) / steps
+    clocks = None
+    if sampler is not None:
+        if ms_step * steps < 250.0 and not case.decode:
+            # the timed region was shorter than a few sampling periods: repeat the same loop, untimed
+            # (the same number of steps on every rank), and take the clocks from both together
+            for _ in range(int(300.0 / max(ms_step, 1e-3)) + 1):
+                case.run()
+            env.sync_all()
+            clocks = dict(sampler.stop((wall0, time.time())),
+                          note="timed region shorter than 0.25 s: sampled over it and an untimed repeat of the same "
+                               "loop right after it")
+        else:
+            clocks = sampler.stop((wall0, wall1))
     status = case.peer_ctx.status() if case.peer_ctx is not None else 0
     return dict(ms_step=ms_step, gemm_ms=gemm_ms, clocks=clocks, eager_us=eager_us, device_status=status)
 

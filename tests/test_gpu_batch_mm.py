@@ -55,10 +55,10 @@ def test_batch_mm_fp32():
     orc.check_close(out.cpu(), torch.bmm(x, w), 1e-5, "batch_mm fp32")
 
 
-@pytest.mark.parametrize("switch", ["YAMOE_B200_2CTA", "YAMOE_B200_FUSED_GATHER"])
+@pytest.mark.parametrize("switch", ["YAMOE_B200_2CTA=1", "YAMOE_B200_FUSED_GATHER=0"])
 def test_opt_in_kernel_variants_in_subprocess(switch):
-    """The cta_group::2 GEMM and the gather-fused gate_up GEMM are selected by environment
-    variables read once per process."""
+    """The cta_group::2 GEMM and the forward with a separate gather kernel (instead of the gather
+    fused into the gate_up GEMM) are selected by environment variables read once per process."""
     import os
     import subprocess
     import sys
@@ -87,6 +87,7 @@ def test_opt_in_kernel_variants_in_subprocess(switch):
         "print('ok')\n")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, PYTHONPATH=root)
-    env[switch] = "1"
+    name, _, value = switch.partition("=")
+    env[name] = value
     res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0 and "ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

@@ -38,7 +38,8 @@ namespace yb {
 
 constexpr int kUmmaBM = 128;
 constexpr int kUmmaBK = 64;            // 64 bf16 = one 128-byte swizzle row
-constexpr int kUmmaThreads = 192;
+constexpr int kUmmaThreads = 192;          // TMA producer, MMA issuer, four epilogue warps
+constexpr int kUmmaGatherThreads = 128;    // four more warps that gather the A rows when the gather is fused
 constexpr int kUmmaAccStride = 256;    // TMEM columns between the two accumulators
 constexpr int kUmmaMaxExperts = 1024;  // padded row offsets of up to this many experts are cached in shared memory
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
@@ -128,14 +129,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
-// Four rows of a 2D tensor, picked by index, into four consecutive 128-byte shared-memory rows
-// (tensor map box {64, 1}; same swizzled layout as a tiled load of four adjacent rows).
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int c0, int r0, int r1, int r2,
-                                            int r3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+// 16-byte asynchronous copy global -> shared (L2 only); src_bytes = 0 writes zeros instead.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// makes this thread's completed generic-proxy writes to shared memory visible to the async proxy (tcgen05.mma)
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -216,7 +218,9 @@ struct UmmaParams {
   const int32_t* pad_off;
   int uniform_tiles;
   int32_t* header;
-  const int32_t* gather_rows;   // kFwd: source row of every padded row (TMA gather of A), or null
+  const int32_t* gather_rows;   // kFwd: source row of every padded row (gather fused into the A operand), or null
+  const void* gather_src;       //       the un-permuted source rows [*, gather_ld]
+  int64_t gather_ld;
   GemmGate gate;                // see GemmGate
 };
 
@@ -230,7 +234,7 @@ struct UmmaSmem {
 };
 
 template <int MODE, int BN, class Epi>
-__global__ void __launch_bounds__(kUmmaThreads, 1)
+__global__ void __launch_bounds__(kUmmaThreads + kUmmaGatherThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const UmmaParams p, const Epi epi) {
   using SM = UmmaSmem<BN>;
@@ -249,9 +253,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
+  // Gather fused into the A operand: four extra warps copy the tile's rows straight from the
+  // un-permuted source into the swizzled A stage (cp.async), the TMA producer loads only B, and a
+  // stage is full after the producer's arrival plus one per gather warp.
+  const bool gather = MODE == kFwd && p.gather_rows != nullptr;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kUmmaStages; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_full[s]), gather ? 1 + kUmmaGatherThreads / 32 : 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -305,7 +313,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (uniform) {
       if (threadIdx.x == 0) { s_pad[0] = 0; s_pad[1] = p.uniform_tiles * kTileM; }
     } else {
-      for (int i = threadIdx.x; i <= p.E; i += kUmmaThreads) s_pad[i] = p.pad_off[i];
+      for (int i = threadIdx.x; i <= p.E; i += blockDim.x) s_pad[i] = p.pad_off[i];
     }
     __syncthreads();
   }
@@ -354,48 +362,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // =========================== TMA producer ================================================
-    if (MODE == kFwd && p.gather_rows != nullptr) {
-      // Gather-fused A operand: the whole warp works.  Lane j fetches rows 4j..4j+3 of the tile
-      // straight from the un-permuted source with one TMA gather per k-block; lane 0 also arms the
-      // barrier and loads B.  The permuted activations never exist in global memory.
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int e_next = expert_of(blockIdx.x);
-      for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
-        int e, row0, n0, krow, kblocks;
-        decode(id, e_next, e, row0, n0, krow, kblocks);
-        e_next = expert_of(id + gridDim.x);
-        const int nboxes = (min(BN, p.N - n0) + 63) >> 6;
-        int4 r = *reinterpret_cast<const int4*>(p.gather_rows + row0 + 4 * lane);
-        r.x = max(r.x, 0); r.y = max(r.y, 0); r.z = max(r.z, 0); r.w = max(r.w, 0);   // padding rows: any valid row
-        for (int kb = 0; kb < kblocks; ++kb) {
-          int good = 1;
-          if (lane == 0) good = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag) ? 1 : 0;
-          good = __shfl_sync(0xffffffffu, good, 0);
-          if (!good) {
-            if (lane == 0) {
-              abort_flag = 1;
-              atomicMax(p.header + kHdrStatus, (int)kStatusProducerTimeout);
-            }
-            ok = false;
-            break;
-          }
-          const uint32_t full = smem_u32(&bar_full[stage]);
-          const uint32_t sa = smem_base + stage * SM::kStageBytes;
-          const uint32_t sb = sa + SM::kABytes;
-          if (lane == 0) {
-            mbar_expect_tx(full, SM::kABytes + nboxes * 8192);
-#pragma unroll
-            for (int i = 0; i < BN / 64; ++i)
-              if (i < nboxes) tma_load_3d(sb + i * 8192, &tmB, n0 + i * 64, kb * kUmmaBK, e, full);
-          }
-          __syncwarp();
-          tma_gather4(sa + lane * 512, &tmA, kb * kUmmaBK, r.x, r.y, r.z, r.w, full);
-          if (++stage == kUmmaStages) { stage = 0; phase ^= 1u; }
-        }
-      }
-    } else if (lane == 0) {
+    if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -410,7 +377,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // MN-major B arrives as 64-column boxes: the last column tile asks only for those it has.
         // (The K-major B of the data gradients is one box of BN rows; rows past N read as zeros.)
         const int nboxes = MODE == kDgrad ? BN / 64 : (min(BN, p.N - n0) + 63) >> 6;
-        const uint32_t stage_tx = SM::kABytes + nboxes * 8192;
+        const uint32_t stage_tx = (gather ? 0 : SM::kABytes) + nboxes * 8192;
         if (MODE == kFwd && p.gate.arrived != nullptr && e != gate_done) {
           // the A rows of this group come from other GPUs: all of them must have landed
           const int need = p.gate.needed[e];
@@ -455,7 +422,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int i = 0; i < BN / 64; ++i)
               if (i < nboxes) tma_load_2d(sb + i * 8192, &tmB, n0 + i * 64, r, full);
           } else {
-            tma_load_2d(sa, &tmA, kb * kUmmaBK, row0, full);
+            if (!gather) tma_load_2d(sa, &tmA, kb * kUmmaBK, row0, full);
             if constexpr (MODE == kFwd) {
 #pragma unroll
               for (int i = 0; i < BN / 64; ++i)
@@ -542,6 +509,76 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       YB_PROF_FLUSH(2, prof_full)
       YB_PROF_FLUSH(3, prof_tmem)
       YB_PROF_FLUSH(4, prof_all)
+    }
+    __syncwarp();
+  } else if (warp >= kUmmaThreads / 32) {
+    // =========================== A-row gather (warps 6..9, only launched when gathering) ========
+    // Warp g copies rows 32g .. 32g+31 of the tile: eight lanes cover the 128 bytes one row
+    // contributes to a 64-deep k-block, so an instruction fetches four full 128-byte lines.  The
+    // 16-byte piece c of row r lands at piece (c ^ (r & 7)) of that row: the 128-byte swizzle
+    // the MMA's descriptor expects (what a tiled TMA load would have produced).  Copies are
+    // asynchronous; three k-blocks are kept in flight per warp, and a k-block is announced on the
+    // stage's full barrier once its copies have completed and a proxy fence has made them visible
+    // to the tensor core.
+    if constexpr (MODE == kFwd) {
+      if (gather) {
+        constexpr int kInFlight = 3;
+        const int gw = warp - kUmmaThreads / 32;
+        const int piece = lane & 7, sub = lane >> 3;
+        const char* src = reinterpret_cast<const char*>(p.gather_src);
+        const size_t row_bytes = (size_t)p.gather_ld * 2;
+        int stage = 0, arr_stage = 0, pending = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        int e_next = expert_of(blockIdx.x);
+        for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
+          int e, row0, n0, krow, kblocks;
+          decode(id, e_next, e, row0, n0, krow, kblocks);
+          e_next = expert_of(id + gridDim.x);
+          int tok[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) tok[i] = __ldg(p.gather_rows + row0 + gw * 32 + i * 4 + sub);
+          for (int kb = 0; kb < kblocks; ++kb) {
+            int good = 1;
+            if (lane == 0) good = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag) ? 1 : 0;
+            good = __shfl_sync(0xffffffffu, good, 0);
+            if (!good) {
+              if (lane == 0) {
+                abort_flag = 1;
+                atomicMax(p.header + kHdrStatus, (int)kStatusProducerTimeout);
+              }
+              ok = false;
+              break;
+            }
+            const uint32_t sa = smem_base + stage * SM::kStageBytes;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = gw * 32 + i * 4 + sub;
+              const bool real = tok[i] >= 0;                       // padding rows are written as zeros
+              cp_async_16(sa + r * 128 + ((piece ^ (r & 7)) << 4),
+                          src + (real ? (size_t)tok[i] * row_bytes + (size_t)kb * 128 + piece * 16 : 0), real ? 16u : 0u);
+            }
+            cp_async_commit();
+            if (++pending == kInFlight) {
+              cp_async_wait<kInFlight - 1>();
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&bar_full[arr_stage]));
+              if (++arr_stage == kUmmaStages) arr_stage = 0;
+              --pending;
+            }
+            if (++stage == kUmmaStages) { stage = 0; phase ^= 1u; }
+          }
+        }
+        cp_async_wait<0>();                 // nothing of this warp is in flight past this point
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (ok && lane == 0)
+          for (; pending > 0; --pending) {
+            mbar_arrive(smem_u32(&bar_full[arr_stage]));
+            if (++arr_stage == kUmmaStages) arr_stage = 0;
+          }
+      }
     }
     __syncwarp();
   } else {
@@ -767,6 +804,7 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
   if (!umma_available()) return YAMOE_ERR_UNSUPPORTED;
   CUtensorMap tmA, tmB;
   bool ok = true;
+  const bool gather = MODE == kFwd && g.gather_rows != nullptr;
   if (MODE == kWgrad) {
     const uint64_t da[2] = {(uint64_t)g.M, (uint64_t)max_rows}, sa[1] = {(uint64_t)g.lda * 2};
     const uint32_t ba[2] = {64, 64};
@@ -774,11 +812,11 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
     const uint64_t db[2] = {(uint64_t)g.N, (uint64_t)max_rows}, sb[1] = {(uint64_t)g.ldb * 2};
     ok = ok && make_map(&tmB, g.B, 2, db, sb, ba);
   } else {
-    const bool gather = MODE == kFwd && g.gather_rows != nullptr;
-    const uint64_t da[2] = {(uint64_t)g.K, (uint64_t)(gather ? g.gather_src_rows : max_rows)};
+    const uint64_t da[2] = {(uint64_t)g.K, (uint64_t)max_rows};
     const uint64_t sa[1] = {(uint64_t)g.lda * 2};
-    const uint32_t ba[2] = {64, gather ? 1u : 128u};      // gather: one row per index, four indices per copy
-    ok = ok && make_map(&tmA, g.A, 2, da, sa, ba);
+    const uint32_t ba[2] = {64, 128u};
+    // with the gather fused, A is read by the gather warps: no map of it is needed
+    if (!gather) ok = ok && make_map(&tmA, g.A, 2, da, sa, ba);
     if (MODE == kFwd) {
       const uint64_t db[3] = {(uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.E};
       const uint64_t sb[2] = {(uint64_t)g.ldb * 2, (uint64_t)g.b_expert_stride * 2};
@@ -792,6 +830,7 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
     }
   }
   if (!ok) return YAMOE_ERR_CUDA;
+  if (gather) tmA = tmB;              // placeholder for the unused kernel parameter
   auto kern = umma_gemm_kernel<MODE, BN, Epi>;
   static bool attr_done = false;   // per template instantiation
   if (!attr_done) {
@@ -800,13 +839,14 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
     attr_done = true;
   }
   UmmaParams p{g.M, g.N, g.K, g.E, g.tile_expert, g.pad_off, (int)max_tiles, const_cast<int32_t*>(g.header),
-               MODE == kFwd ? g.gather_rows : nullptr, g.gate};
+               gather ? g.gather_rows : nullptr, g.A, g.lda, g.gate};
   const int NT = (int)ceil_div(g.N, BN);
   int64_t total_max = MODE == kWgrad ? (int64_t)g.E * ceil_div(g.M, kUmmaBM) * NT : max_tiles * NT;
   int grid = (int)std::min<int64_t>(total_max, umma_sm_count());
   if (grid <= 0) return YAMOE_OK;
   // a gated GEMM is meant to start while its predecessor on the stream still runs
-  if (launch_pdl_opt(g.gate.prep != nullptr, kern, dim3(grid), dim3(kUmmaThreads), SM::kTotal, stream, tmA, tmB, p, epi) !=
+  const int threads = kUmmaThreads + (gather ? kUmmaGatherThreads : 0);
+  if (launch_pdl_opt(g.gate.prep != nullptr, kern, dim3(grid), dim3(threads), SM::kTotal, stream, tmA, tmB, p, epi) !=
       cudaSuccess)
     return YAMOE_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
