@@ -98,6 +98,21 @@ inline bool pdl_enabled(bool default_on = false) {
   return v < 0 ? default_on : v != 0;
 }
 
+// Function attributes and device properties belong to one device; a process may drive several.
+constexpr int kMaxDevices = 64;
+inline int current_device_index() {
+  int dev = 0;
+  return cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices ? dev : 0;
+}
+// A value remembered per device (for instance the dynamic shared memory a kernel was configured
+// for); zero-initialised, so "0" has to mean "not set yet".
+template <typename V>
+struct PerDevice {
+  std::atomic<V> v[kMaxDevices] = {};
+  V get(int dev) const { return v[dev].load(std::memory_order_acquire); }
+  void set(int dev, V x) { v[dev].store(x, std::memory_order_release); }
+};
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl_opt(bool default_on, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                   cudaStream_t st, Args&&... args) {

@@ -152,7 +152,9 @@ struct EpiGlu {
     if (pad && pre != nullptr) store_vec<T, NV>(pre + (size_t)row * 2 * H + n0, p);
     if (act != nullptr) store_vec<T, NV / 2>(act + (size_t)row * H + n0 / 2, a);
     if (actw != nullptr) {
-      const float w = pad ? 0.f : row_weight[row];
+      // read past L1: on the expert-parallel path the weights are stored by other GPUs while this
+      // kernel is already resident
+      const float w = pad ? 0.f : __ldcg(row_weight + row);
       const int ld = actw_ld > 0 ? actw_ld : H;
 #pragma unroll
       for (int i = 0; i < NV / 2; ++i) a[i] *= w;

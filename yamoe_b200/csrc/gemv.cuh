@@ -348,11 +348,12 @@ inline int launch_gemv_stage(const GemvArgs& g, cudaStream_t st, int ksplit = 1)
   size_t smem = (((size_t)kGemvMT * g.Kdim * 2 + 15) & ~size_t(15)) + (size_t)NPART * kGemvMT * NB * 4 +
                 (size_t)g.E * 4 + 2 * kGemvMaxS * 4;
   auto kern = gemv_kernel<STAGE, NB>;
-  static size_t configured = 0;
-  if (smem > configured) {
+  static PerDevice<size_t> configured;   // per template instantiation and device
+  const int dev = current_device_index();
+  if (smem > configured.get(dev)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return YAMOE_ERR_UNSUPPORTED;
-    configured = smem;
+    configured.set(dev, smem);
   }
   const int slots = g.E < g.S ? g.E : g.S;
   dim3 grid((unsigned)slots, (unsigned)ceil_div(g.N, NB), (unsigned)(STAGE == kDown ? ksplit : 1));

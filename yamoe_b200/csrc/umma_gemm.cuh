@@ -702,6 +702,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
+  // A gated kernel ran next to its predecessor; it ends only once that kernel has ended, so that
+  // "this kernel is complete" keeps implying "everything before it on the stream is complete".
+  if (gated) pdl_wait();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -723,7 +726,21 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-inline bool umma_available() { return encode_tiled_fn() != nullptr; }
+// The tcgen05 kernels need the driver's tensor-map encoder and a device of compute capability 10.x
+// (the library is built for sm_100a only, but the check keeps the answer honest per device).
+inline bool umma_available() {
+  if (encode_tiled_fn() == nullptr) return false;
+  static PerDevice<int> major_plus_1;
+  const int dev = current_device_index();
+  int m = major_plus_1.get(dev);
+  if (m == 0) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) major = 0;
+    m = major + 1;
+    major_plus_1.set(dev, m);
+  }
+  return m - 1 == 10;
+}
 
 // bf16 tensor map with 128-byte swizzle; dims / box innermost first, strides in bytes for dims 1...
 // Encoding a map is a driver call that costs some tens of microseconds of host time; the same
@@ -778,12 +795,13 @@ inline bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t*
 }
 
 inline int umma_sm_count() {
-  static int n = []() {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-    return v;
-  }();
+  static PerDevice<int> count;
+  const int dev = current_device_index();
+  int n = count.get(dev);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    count.set(dev, n);
+  }
   return n;
 }
 
@@ -832,11 +850,12 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
   if (!ok) return YAMOE_ERR_CUDA;
   if (gather) tmA = tmB;              // placeholder for the unused kernel parameter
   auto kern = umma_gemm_kernel<MODE, BN, Epi>;
-  static bool attr_done = false;   // per template instantiation
-  if (!attr_done) {
+  static PerDevice<int> attr_done;   // per template instantiation and device
+  const int dev = current_device_index();
+  if (!attr_done.get(dev)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal) != cudaSuccess)
       return YAMOE_ERR_CUDA;
-    attr_done = true;
+    attr_done.set(dev, 1);
   }
   UmmaParams p{g.M, g.N, g.K, g.E, g.tile_expert, g.pad_off, (int)max_tiles, const_cast<int32_t*>(g.header),
                gather ? g.gather_rows : nullptr, g.A, g.lda, g.gate};

@@ -370,11 +370,12 @@ inline int launch_umma_gemm_2cta(const GemmArgs& g, const Epi& epi, int64_t max_
   }
   if (!ok) return YAMOE_ERR_CUDA;
   auto kern = umma_gemm_2cta_kernel<MODE, Epi>;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDevice<int> attr_done;   // per template instantiation and device
+  const int dev = current_device_index();
+  if (!attr_done.get(dev)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kU2Smem) != cudaSuccess)
       return YAMOE_ERR_CUDA;
-    attr_done = true;
+    attr_done.set(dev, 1);
   }
   Umma2Params p{g.N, g.K, g.E, g.pair_expert, g.pair_off, g.pad_off, const_cast<int32_t*>(g.header)};
   const int NT = (int)ceil_div(g.N, kU2BN);

@@ -549,18 +549,18 @@ template <typename T>
 static int ep_local_backward_impl(const void* recv_x, const void* recv_g, const float* recv_w, const void* wgu,
                                   const void* bgu, const void* wd, const void* bd, void* d_wgu, void* d_bgu,
                                   void* d_wd, void* d_bd, void* const* peer_back_w, int64_t cap, int64_t max_rows,
-                                  int H, int per, int G, int dtype, const EpPlan& p, cudaStream_t st) {
+                                  int H, int per, int G, int dtype, const EpPlan& p, cudaStream_t st,
+                                  const GemmGate& gate = GemmGate{}) {
   const RouteTables& rt = p.t.rt;
   const int64_t max_tiles = max_rows / kTileM;
-  ep_load_weights_kernel<<<(unsigned)ceil_div(max_rows, 256), 256, 0, st>>>(p.t, recv_w, max_rows);
-  gather_grad_kernel<T><<<(unsigned)ceil_div(max_rows, kRowWarps), kRowWarps * 32, 0, st>>>(
-      reinterpret_cast<const T*>(recv_g), 1, reinterpret_cast<const T*>(bd), reinterpret_cast<T*>(p.gys), p.gw_row,
-      rt.row_token, rt.tile_expert, rt.header, H);
   auto with_pairs = [&](GemmArgs g) { g.pair_expert = rt.pair_expert; g.pair_off = rt.pair_off; g.counts = rt.counts; return g; };
+  // p.act receives the activations times the routing weight; the weights are taken from the
+  // receive buffer itself (row_weight is filled from it only after this GEMM)
   EpiGlu<T> glu{reinterpret_cast<const T*>(bgu), nullptr, reinterpret_cast<T*>(p.act), reinterpret_cast<T*>(p.pre),
-                rt.row_token, rt.row_weight, H, 0};
-  const GemmArgs g1 = with_pairs(GemmArgs{recv_x, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, per,
-                                          rt.tile_expert, rt.pad_off, rt.header});
+                rt.row_token, recv_w, H, 0};
+  GemmArgs g1 = with_pairs(GemmArgs{recv_x, H, wgu, 2 * (int64_t)H, (int64_t)H * 2 * H, 0, 2 * H, H, per,
+                                    rt.tile_expert, rt.pad_off, rt.header});
+  g1.gate = gate;
   EpiGluBackward<T> glub{reinterpret_cast<const T*>(p.pre), reinterpret_cast<T*>(p.gpre), p.gw_row, rt.row_token,
                          rt.row_weight, H};
   const GemmArgs g2 = with_pairs(GemmArgs{p.gys, H, wd, H, (int64_t)H * H, 0, H, H, per, rt.tile_expert, rt.pad_off,
@@ -575,16 +575,29 @@ static int ep_local_backward_impl(const void* recv_x, const void* recv_g, const 
   const GemmArgs g5 = with_pairs(GemmArgs{recv_x, H, p.gpre, 2 * (int64_t)H, 0, H, 2 * H, 0, per, rt.tile_expert,
                                           rt.pad_off, rt.header});
   int rc = YAMOE_OK;
-  if (use_tcgen05(current_path(), dtype, H)) {
+  const bool tc = use_tcgen05(current_path(), dtype, H);
+  // The recomputed gate_up GEMM needs only the token rows: it goes first, and with a gate it runs
+  // next to the dispatch kernel, waiting for each expert's rows by itself.  When it has finished,
+  // every row of this rank (token, gradient, weight) has arrived.
+  if (tc) {
     if constexpr (sizeof(T) == 2) {
       if ((rc = launch_umma<kFwd>(g1, glu, max_rows, max_tiles, st))) return rc;
+    }
+  } else {
+    launch_simt_gemm<T, kFwd>(g1, glu, max_rows, st);
+  }
+  ep_load_weights_kernel<<<(unsigned)ceil_div(max_rows, 256), 256, 0, st>>>(p.t, recv_w, max_rows);
+  gather_grad_kernel<T><<<(unsigned)ceil_div(max_rows, kRowWarps), kRowWarps * 32, 0, st>>>(
+      reinterpret_cast<const T*>(recv_g), 1, reinterpret_cast<const T*>(bd), reinterpret_cast<T*>(p.gys), p.gw_row,
+      rt.row_token, rt.tile_expert, rt.header, H);
+  if (tc) {
+    if constexpr (sizeof(T) == 2) {
       if ((rc = launch_umma<kDgrad>(g2, glub, max_rows, max_tiles, st))) return rc;
       if ((rc = launch_umma<kWgrad>(g3, st_wd, max_rows, max_tiles, st))) return rc;
       if ((rc = launch_umma<kDgrad>(g4, prows, max_rows, max_tiles, st))) return rc;
       if ((rc = launch_umma<kWgrad>(g5, st_wgu, max_rows, max_tiles, st))) return rc;
     }
   } else {
-    launch_simt_gemm<T, kFwd>(g1, glu, max_rows, st);
     launch_simt_gemm<T, kDgrad>(g2, glub, max_rows, st);
     launch_simt_gemm<T, kWgrad>(g3, st_wd, max_rows, st);
     launch_simt_gemm<T, kDgrad>(g4, prows, max_rows, st);
@@ -683,18 +696,30 @@ static int ep_call_prologue(const yamoe_ep_ctx_t& c, const EpCallPlan& p, const 
   a.S = (int)S; a.H = c.H; a.E = c.E; a.G = c.G; a.rank = c.rank; a.K = c.K;
   a.signal_rows = gate != nullptr ? 1 : 0;
   a.wait_ns = wait_ns;
-  // Next to a GEMM CTA an SM has registers for two of these CTAs; alone, for four.  The kernel asks
-  // for the same (maximal) shared-memory carve-out as the GEMM: CTAs of kernels with different
-  // carve-outs do not share an SM.
+  // Alone the kernel fills the GPU (four CTAs per SM).  Next to the gated GEMM it runs with one CTA
+  // on every second SM (YAMOE_B200_EP_DISPATCH_CTAS overrides the number): that many warps still
+  // saturate NVLink, they take little from the GEMM, and - what matters most - few enough rows are
+  // in flight at a time that the experts really complete in phase order; with hundreds of CTAs
+  // every phase is issued at once and the first expert is complete only when nearly all are.
+  // Measured on 2 GPUs, weak-scaled forward: 0.925 ms with 296 CTAs, 0.879 with 148, 0.869 with 74,
+  // 0.881 with 37, 1.12 with 18; 0.927 without overlap.  The kernel asks for the same (maximal)
+  // shared-memory carve-out as the GEMM: CTAs of kernels with different carve-outs do not share an SM.
+  static const int grid_cap_env = []() {
+    const char* env = std::getenv("YAMOE_B200_EP_DISPATCH_CTAS");
+    return env != nullptr ? std::atoi(env) : 0;
+  }();
+  const int64_t grid_cap = gate == nullptr      ? (int64_t)umma_sm_count() * 4
+                           : grid_cap_env > 0 ? grid_cap_env
+                                              : std::max(1, umma_sm_count() / 2);
   const int grid = (int)std::max<int64_t>(
-      1, std::min<int64_t>(std::max<int64_t>(ceil_div(S, kRowWarps * 4), ceil_div(c.max_rows, 4096)),
-                           (int64_t)umma_sm_count() * (gate != nullptr ? 2 : 4)));
+      1, std::min<int64_t>(std::max<int64_t>(ceil_div(S, kRowWarps * 4), ceil_div(c.max_rows, 4096)), grid_cap));
   {
-    static std::atomic<bool> carveout_set{false};    // per template instantiation
-    if (!carveout_set.load()) {
+    static PerDevice<int> carveout_set;    // per template instantiation and device
+    const int dev = current_device_index();
+    if (!carveout_set.get(dev)) {
       cudaFuncSetAttribute(ep_dispatch_fused_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout,
                            (int)cudaSharedmemCarveoutMaxShared);
-      carveout_set.store(true);
+      carveout_set.set(dev, 1);
     }
   }
   ep_dispatch_fused_kernel<T><<<grid, kRowWarps * 32, (size_t)(6 * c.E + 2) * sizeof(int32_t), st>>>(a, p.ep.t);
@@ -712,6 +737,17 @@ static int ep_call_prologue(const yamoe_ep_ctx_t& c, const EpCallPlan& p, const 
   return cudaGetLastError() == cudaSuccess ? YAMOE_OK : YAMOE_ERR_CUDA;
 }
 
+// The gate_up GEMM (the recomputed one in the backward pass) overlaps the dispatch when it is the
+// tcgen05 kernel; YAMOE_B200_EP_OVERLAP=0 keeps the two apart (dispatch, wait for all sources,
+// then the GEMMs).
+static bool ep_overlap_enabled() {
+  static const bool on = []() {
+    const char* env = std::getenv("YAMOE_B200_EP_OVERLAP");
+    return env == nullptr || std::atoi(env) != 0;
+  }();
+  return on;
+}
+
 template <typename T>
 static int ep_forward_impl(const yamoe_ep_ctx_t& c, const void* hidden, const int64_t* ridx, const void* rw,
                            int rcols, const void* wgu, const void* bgu, const void* wd, const void* bd, void* out,
@@ -720,13 +756,7 @@ static int ep_forward_impl(const yamoe_ep_ctx_t& c, const void* hidden, const in
   const EpCtrlLayout lay{c.G, c.E};
   const uint64_t wait_ns = c.wait_ns ? c.wait_ns : kWaitLimitNs;
   int rc;
-  // The gate_up GEMM overlaps the dispatch when it is the tcgen05 kernel; YAMOE_B200_EP_OVERLAP=0
-  // keeps the two apart (dispatch, wait for all sources, then the GEMMs).
-  static const bool overlap_env = []() {
-    const char* env = std::getenv("YAMOE_B200_EP_OVERLAP");
-    return env == nullptr || std::atoi(env) != 0;
-  }();
-  const bool overlap = overlap_env && sizeof(T) == 2 && use_tcgen05(current_path(), c.dtype, c.H);
+  const bool overlap = ep_overlap_enabled() && sizeof(T) == 2 && use_tcgen05(current_path(), c.dtype, c.H);
   GemmGate gate;
   {
     StageTimer tm(kStageEpDispatch, st);
@@ -759,11 +789,14 @@ static int ep_backward_impl(const yamoe_ep_ctx_t& c, const void* grad_out, const
   const EpCtrlLayout lay{c.G, c.E};
   const uint64_t wait_ns = c.wait_ns ? c.wait_ns : kWaitLimitNs;
   const int64_t S = Tn * c.K;
-  int rc = ep_call_prologue<T>(c, p, hidden, grad_out, ridx, rw, rcols, Tn, cap, c.peer_back, st);
+  const bool overlap = ep_overlap_enabled() && sizeof(T) == 2 && use_tcgen05(current_path(), c.dtype, c.H);
+  GemmGate gate;
+  int rc = ep_call_prologue<T>(c, p, hidden, grad_out, ridx, rw, rcols, Tn, cap, c.peer_back, st,
+                               overlap ? &gate : nullptr);
   if (rc) return rc;
   rc = ep_local_backward_impl<T>(c.recv_x, c.recv_g, reinterpret_cast<const float*>(c.recv_w), wgu, bgu, wd, bd,
                                  d_wgu, d_bgu, d_wd, d_bd, c.peer_back_w, cap, c.max_rows, c.H, c.E / c.G, c.G,
-                                 c.dtype, p.ep, st);
+                                 c.dtype, p.ep, st, gate);
   if (rc) return rc;
   ep_signal_kernel<<<1, 32, 0, st>>>(c.peer_ctrl, lay.flag_return(), c.G, c.rank,
                                      reinterpret_cast<const int32_t*>(c.state));
