@@ -63,12 +63,15 @@ def test_router_topk_kernel():
 def test_router_forward_matches_linear_topk_softmax():
     """Router projection + top-k + softmax + scatter in the library against the reference layer's
     chain (torch-ext/yamoe/layers.py:126-149) in torch: fp32 through the CUDA-core GEMM and the top-k
-    kernel, bf16 through the single tcgen05 kernel (H a multiple of 64) and through the two-kernel
-    form (H = 72)."""
+    kernel, bf16 through the single tcgen05 kernel (H a multiple of 64, K <= 8; one and four column
+    chunks per row), through the two-kernel form (H = 72, or K = 12), and both types through the
+    one-CTA-per-token kernel (T <= 64)."""
     import yamoe_b200
     for T, H, E, K, dtype in ((300, 256, 32, 4, torch.float32), (1, 128, 8, 2, torch.float32),
                               (1000, 2880, 32, 4, torch.bfloat16), (130, 256, 128, 4, torch.bfloat16),
-                              (5, 128, 48, 3, torch.bfloat16), (64, 72, 16, 2, torch.bfloat16)):
+                              (5, 128, 48, 3, torch.bfloat16), (64, 72, 16, 2, torch.bfloat16),
+                              (200, 72, 16, 2, torch.bfloat16), (200, 256, 64, 12, torch.bfloat16),
+                              (4, 2880, 128, 4, torch.bfloat16), (129, 128, 40, 8, torch.bfloat16)):
         gen = torch.Generator().manual_seed(T + E)
         x = torch.randn(T, H, generator=gen).to(dtype)
         w = (torch.randn(E, H, generator=gen) / H ** 0.5).to(dtype)
