@@ -229,7 +229,11 @@ struct UmmaSmem {
   static constexpr int kABytes = kUmmaBM * 128;
   static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
+#ifdef YB_STAGES
+  static constexpr int kStages = YB_STAGES;                         // timing experiments only
+#else
   static constexpr int kStages = (227 * 1024 - 8192) / kStageBytes;  // 6 / 5 / 4 stages for BN 128 / 192 / 256
+#endif
   static constexpr int kTotal = kStages * kStageBytes + 1024;       // + slack for 1024-byte alignment
 };
 
