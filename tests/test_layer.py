@@ -136,6 +136,35 @@ def test_router_topk_non_finite_logits():
 
 
 @pytest.mark.gpu
+def test_router_forward_non_finite_inputs():
+    """NaN and infinite activations through the fused router kernels (few-token form, tensor-core
+    form with one and with four column chunks): K distinct valid experts per row, finite rows
+    untouched by their neighbours, nothing written outside the outputs."""
+    import yamoe_b200
+    for T, H, E, K in ((8, 128, 16, 4), (200, 128, 32, 4), (200, 128, 128, 4)):
+        gen = torch.Generator().manual_seed(T + E)
+        x = torch.randn(T, H, generator=gen).bfloat16()
+        w = (torch.randn(E, H, generator=gen) / H ** 0.5).bfloat16()
+        b = (torch.randn(E, generator=gen) * 0.1).bfloat16()
+        x[0] = float("nan")                        # every logit of the row is NaN
+        x[1, 7] = float("inf")                     # logits are +inf, -inf or NaN depending on the weight's sign
+        idx, scores = yamoe_b200.router_forward(x.cuda(), w.cuda(), b.cuda(), K)
+        torch.cuda.synchronize()
+        idx, scores = idx.cpu(), scores.float().cpu()
+        assert ((idx >= 0) & (idx < E)).all(), (T, E, idx[:2])
+        for t in range(T):
+            assert len(set(idx[t].tolist())) == K, (T, E, t, idx[t])
+        clean = torch.ones(T, dtype=torch.bool); clean[:2] = False
+        assert torch.isfinite(scores[clean]).all()
+        assert ((scores[clean].sum(1) - 1).abs() <= 2e-2).all()
+        assert int((scores[clean] != 0).sum(1).max()) <= K
+        logits = torch.nn.functional.linear(x[clean].cuda(), w.cuda(), b.cuda()).float().cpu()
+        top_v = torch.topk(logits, K, dim=-1).values
+        got_v = torch.gather(logits, 1, idx[clean])
+        assert (got_v.sort(1, descending=True).values - top_v).abs().max() <= 2e-2 * logits.abs().max()
+
+
+@pytest.mark.gpu
 def test_yamoe_module_matches_reference_mlp():
     g, T, H, E, K = _golden_layer()
     m = _module(g, E, K, capacity=T)
