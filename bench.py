@@ -590,9 +590,10 @@ def time_e2e(case: Case, steps: int, warmup: int, eager: bool):
 
     # Three streams pipeline consecutive steps: while step i computes, step i+1's inputs come in and
     # step i-1's result goes out (PCIe is full duplex).  Every step still copies its own inputs from
-    # pinned host memory and its own result back; expert-parallel steps stay on one stream because
-    # all calls of a rank share its peer-writable buffers.
-    pipelined = not case.use_ep
+    # pinned host memory and its own result back.  Expert-parallel steps pipeline the same way: their
+    # calls stay in order on the compute stream (all calls of a rank share its peer-writable
+    # buffers), only the copies of the neighbouring steps move to the other two streams.
+    pipelined = True
     cur = torch.cuda.current_stream()
     s_in, s_out = (torch.cuda.Stream(), torch.cuda.Stream()) if pipelined else (cur, cur)
     host_outs = [host_out, torch.empty_like(host_out).pin_memory()]
@@ -629,7 +630,7 @@ def time_e2e(case: Case, steps: int, warmup: int, eager: bool):
     # cannot fall behind the GPU.  Three graphs with their own buffers take turns on three streams,
     # so consecutive steps overlap as in the eager pipeline.  Anything else keeps the eager pipeline.
     graphs = None
-    if pipelined and w["mode"] == "fwd" and not eager:
+    if not case.use_ep and w["mode"] == "fwd" and not eager:
         try:
             graphs = []
             g_streams = [s_in, s_out, torch.cuda.Stream()]

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 REL = os.path.join("build", "torch28-cxx11-cu129-x86_64-linux", "yamoe", "reference.py")
 
 
-def make_ref(root: str = "/root/reference") -> str | None:
+def make_ref(root: str = os.environ.get("YAMOE_REFERENCE_ROOT", "/root/reference")) -> str | None:
     src = os.path.join(root, REL)
     if not os.path.exists(src):
         return None
