@@ -73,13 +73,12 @@ TRAFFIC = {
 }
 
 # kernels of this library launched by one call (memsets not counted):
-#   fwd     2 routing + gate_up GEMM (gathers its rows itself) + down GEMM + combine
+#   fwd     2 routing + row gather + gate_up GEMM + down GEMM + combine
 #   bwd     2 routing + 2 gathers + 5 GEMMs (bias gradients ride along) + routing gradient + cast
 #   ep_fwd  2 routing + publish + dispatch + 2 GEMMs + signal + combine
 #   ep_bwd  2 routing + publish + dispatch + weights + gather + 5 GEMMs + 2 column sums +
 #           scalar return + signal + combine + routing gradient
-# fp32 forward adds the separate row gather (the fused gather is part of the tcgen05 kernel).
-LAUNCHES = {"fwd": 5, "fwd_fp32": 6, "bwd": 11, "train": 16, "decode": 2, "ep_fwd": 8, "ep_bwd": 17}
+LAUNCHES = {"fwd": 6, "fwd_fp32": 6, "bwd": 11, "train": 17, "decode": 2, "ep_fwd": 8, "ep_bwd": 17}
 
 
 def measured_peaks():

@@ -55,10 +55,11 @@ def test_batch_mm_fp32():
     orc.check_close(out.cpu(), torch.bmm(x, w), 1e-5, "batch_mm fp32")
 
 
-@pytest.mark.parametrize("switch", ["YAMOE_B200_2CTA=1", "YAMOE_B200_FUSED_GATHER=0"])
+@pytest.mark.parametrize("switch", ["YAMOE_B200_2CTA=1", "YAMOE_B200_FUSED_GATHER=1", "YAMOE_B200_WIDE_TMA=0"])
 def test_opt_in_kernel_variants_in_subprocess(switch):
-    """The cta_group::2 GEMM and the forward with a separate gather kernel (instead of the gather
-    fused into the gate_up GEMM) are selected by environment variables read once per process."""
+    """The cta_group::2 GEMM, the forward with the gather fused into the gate_up GEMM (instead of the
+    separate gather kernel) and the GEMMs with one TMA copy per 64-column box (instead of one per
+    operand) are selected by environment variables read once per process."""
     import os
     import subprocess
     import sys

@@ -177,6 +177,7 @@ struct EpiGlu {
 // T = 4096), so it is off.
 template <typename T>
 struct EpiGluAct {
+  static constexpr bool kMayGather = true;     // the forward's gate_up GEMM may gather its A rows itself
   static constexpr bool kStagedRows = false;
   static constexpr int kOutPerChunk = 16;
   const T* bias;             // [E, 2H]

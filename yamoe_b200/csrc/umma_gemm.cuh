@@ -138,6 +138,12 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 // makes this thread's completed generic-proxy writes to shared memory visible to the async proxy (tcgen05.mma)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -206,6 +212,13 @@ struct epi_prefetches : std::false_type {};
 template <class E>
 struct epi_prefetches<E, std::enable_if_t<E::kPrefetchTile>> : std::true_type {};
 
+// Forward epilogues that declare `static constexpr bool kMayGather = true` also get the kernel
+// instantiation whose extra warps gather the A rows (one more kernel per such functor).
+template <class E, class = void>
+struct epi_gathers : std::false_type {};
+template <class E>
+struct epi_gathers<E, std::enable_if_t<E::kMayGather>> : std::true_type {};
+
 template <class E, class = void>
 struct epi_staged : std::false_type {};
 template <class E>
@@ -222,6 +235,11 @@ struct UmmaParams {
   const void* gather_src;       //       the un-permuted source rows [*, gather_ld]
   int64_t gather_ld;
   GemmGate gate;                // see GemmGate
+  // MN-major operands whose width is a multiple of 64 are described as (64 columns, rows, column
+  // block[, expert]) so that ONE copy brings all the 64-column boxes of a stage (box 64 x 64 x BN/64):
+  // the producer thread issues two copies per k-block instead of five (forward) or six (weight
+  // gradient), and the last box lands earlier
+  int a_wide, b_wide;
 };
 
 template <int BN>
@@ -237,8 +255,10 @@ struct UmmaSmem {
   static constexpr int kTotal = kStages * kStageBytes + 1024;       // + slack for 1024-byte alignment
 };
 
-template <int MODE, int BN, class Epi>
-__global__ void __launch_bounds__(kUmmaThreads + kUmmaGatherThreads, 1)
+// GATHER (kFwd only): the kernel is launched with four more warps that fetch the A rows themselves
+// (see "A-row gather" below); without it the kernel has six warps and no trace of that role.
+template <int MODE, int BN, class Epi, bool GATHER = false>
+__global__ void __launch_bounds__(kUmmaThreads + (GATHER ? kUmmaGatherThreads : 0), 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const UmmaParams p, const Epi epi) {
   using SM = UmmaSmem<BN>;
@@ -260,7 +280,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // Gather fused into the A operand: four extra warps copy the tile's rows straight from the
   // un-permuted source into the swizzled A stage (cp.async), the TMA producer loads only B, and a
   // stage is full after the producer's arrival plus one per gather warp.
-  const bool gather = MODE == kFwd && p.gather_rows != nullptr;
+  constexpr bool gather = GATHER && MODE == kFwd;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kUmmaStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), gather ? 1 + kUmmaGatherThreads / 32 : 1);
@@ -381,7 +401,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // MN-major B arrives as 64-column boxes: the last column tile asks only for those it has.
         // (The K-major B of the data gradients is one box of BN rows; rows past N read as zeros.)
         const int nboxes = MODE == kDgrad ? BN / 64 : (min(BN, p.N - n0) + 63) >> 6;
-        const uint32_t stage_tx = (gather ? 0 : SM::kABytes) + nboxes * 8192;
+        const uint32_t stage_tx = (gather ? 0 : SM::kABytes) + (p.b_wide ? BN / 64 : nboxes) * 8192;
         if (MODE == kFwd && p.gate.arrived != nullptr && e != gate_done) {
           // the A rows of this group come from other GPUs: all of them must have landed
           const int need = p.gate.needed[e];
@@ -420,17 +440,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(full, stage_tx);
           if constexpr (MODE == kWgrad) {
             const int r = krow + kb * kUmmaBK;
+            if (p.a_wide) {
+              tma_load_3d(sa, &tmA, 0, r, row0 >> 6, full);
+            } else {
 #pragma unroll
-            for (int i = 0; i < kUmmaBM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, row0 + i * 64, r, full);
+              for (int i = 0; i < kUmmaBM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, row0 + i * 64, r, full);
+            }
+            if (p.b_wide) {
+              tma_load_3d(sb, &tmB, 0, r, n0 >> 6, full);
+            } else {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i)
-              if (i < nboxes) tma_load_2d(sb + i * 8192, &tmB, n0 + i * 64, r, full);
+              for (int i = 0; i < BN / 64; ++i)
+                if (i < nboxes) tma_load_2d(sb + i * 8192, &tmB, n0 + i * 64, r, full);
+            }
           } else {
             if (!gather) tma_load_2d(sa, &tmA, kb * kUmmaBK, row0, full);
             if constexpr (MODE == kFwd) {
+              if (p.b_wide) {
+                tma_load_4d(sb, &tmB, 0, kb * kUmmaBK, n0 >> 6, e, full);
+              } else {
 #pragma unroll
-              for (int i = 0; i < BN / 64; ++i)
-                if (i < nboxes) tma_load_3d(sb + i * 8192, &tmB, n0 + i * 64, kb * kUmmaBK, e, full);
+                for (int i = 0; i < BN / 64; ++i)
+                  if (i < nboxes) tma_load_3d(sb + i * 8192, &tmB, n0 + i * 64, kb * kUmmaBK, e, full);
+              }
             } else {
               tma_load_3d(sb, &tmB, kb * kUmmaBK, n0, e, full);
             }
@@ -515,7 +547,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       YB_PROF_FLUSH(4, prof_all)
     }
     __syncwarp();
-  } else if (warp >= kUmmaThreads / 32) {
+  } else if (gather && warp >= kUmmaThreads / 32) {
     // =========================== A-row gather (warps 6..9, only launched when gathering) ========
     // Warp g copies rows 32g .. 32g+31 of the tile: eight lanes cover the 128 bytes one row
     // contributes to a 64-deep k-block, so an instruction fetches four full 128-byte lines.  The
@@ -524,8 +556,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // asynchronous; three k-blocks are kept in flight per warp, and a k-block is announced on the
     // stage's full barrier once its copies have completed and a proxy fence has made them visible
     // to the tensor core.
-    if constexpr (MODE == kFwd) {
-      if (gather) {
+    if constexpr (gather) {
+      {
         constexpr int kInFlight = 3;
         const int gw = warp - kUmmaThreads / 32;
         const int piece = lane & 7, sub = lane >> 3;
@@ -708,7 +740,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
   // A gated kernel ran next to its predecessor; it ends only once that kernel has ended, so that
   // "this kernel is complete" keeps implying "everything before it on the stream is complete".
+#ifndef YB_NO_END_WAIT
   if (gated) pdl_wait();
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -753,8 +787,8 @@ inline bool umma_available() {
 struct TensorMapKey {
   const void* base;
   int rank;
-  uint64_t dims[3], strides[2];
-  uint32_t box[3];
+  uint64_t dims[4], strides[3];
+  uint32_t box[4];
   bool operator==(const TensorMapKey& o) const {
     if (base != o.base || rank != o.rank) return false;
     for (int i = 0; i < rank; ++i)
@@ -782,9 +816,9 @@ inline bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t*
     for (int i = 0; i < used; ++i)
       if (keys[i] == key) { *m = maps[i]; return true; }
   }
-  cuuint64_t gd[3];
-  cuuint64_t gs[2];
-  cuuint32_t bx[3], es[3] = {1, 1, 1};
+  cuuint64_t gd[4];
+  cuuint64_t gs[3];
+  cuuint32_t bx[4], es[4] = {1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; }
   for (int i = 0; i + 1 < rank; ++i) gs[i] = strides[i];
   CUresult r = encode_tiled_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gd,
@@ -819,27 +853,55 @@ inline int umma_tile_n() {
   return bn;
 }
 
+template <int MODE, int BN, class Epi, bool GATHER>
+inline int launch_umma_kernel(const GemmArgs& g, const Epi& epi, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                              int64_t max_tiles, bool a_wide, bool b_wide, cudaStream_t stream);
+
 template <int MODE, int BN, class Epi>
 inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_rows, int64_t max_tiles,
                                cudaStream_t stream) {
-  using SM = UmmaSmem<BN>;
   if (!umma_available()) return YAMOE_ERR_UNSUPPORTED;
   CUtensorMap tmA, tmB;
   bool ok = true;
   const bool gather = MODE == kFwd && g.gather_rows != nullptr;
+  // one copy per operand and k-block where the MN-major operand's width allows the blocked view
+  // (YAMOE_B200_WIDE_TMA=0 keeps one copy per 64-column box)
+  static const bool wide_on = []() {
+    const char* env = std::getenv("YAMOE_B200_WIDE_TMA");
+    return env == nullptr || std::atoi(env) != 0;
+  }();
+  const bool a_wide = wide_on && MODE == kWgrad && g.M % 64 == 0;
+  const bool b_wide = wide_on && MODE != kDgrad && g.N % 64 == 0;
   if (MODE == kWgrad) {
-    const uint64_t da[2] = {(uint64_t)g.M, (uint64_t)max_rows}, sa[1] = {(uint64_t)g.lda * 2};
     const uint32_t ba[2] = {64, 64};
-    ok = ok && make_map(&tmA, g.A, 2, da, sa, ba);
-    const uint64_t db[2] = {(uint64_t)g.N, (uint64_t)max_rows}, sb[1] = {(uint64_t)g.ldb * 2};
-    ok = ok && make_map(&tmB, g.B, 2, db, sb, ba);
+    if (a_wide) {
+      const uint64_t da[3] = {64, (uint64_t)max_rows, (uint64_t)g.M / 64}, sa[2] = {(uint64_t)g.lda * 2, 128};
+      const uint32_t bw[3] = {64, 64, kUmmaBM / 64};
+      ok = ok && make_map(&tmA, g.A, 3, da, sa, bw);
+    } else {
+      const uint64_t da[2] = {(uint64_t)g.M, (uint64_t)max_rows}, sa[1] = {(uint64_t)g.lda * 2};
+      ok = ok && make_map(&tmA, g.A, 2, da, sa, ba);
+    }
+    if (b_wide) {
+      const uint64_t db[3] = {64, (uint64_t)max_rows, (uint64_t)g.N / 64}, sb[2] = {(uint64_t)g.ldb * 2, 128};
+      const uint32_t bw[3] = {64, 64, BN / 64};
+      ok = ok && make_map(&tmB, g.B, 3, db, sb, bw);
+    } else {
+      const uint64_t db[2] = {(uint64_t)g.N, (uint64_t)max_rows}, sb[1] = {(uint64_t)g.ldb * 2};
+      ok = ok && make_map(&tmB, g.B, 2, db, sb, ba);
+    }
   } else {
     const uint64_t da[2] = {(uint64_t)g.K, (uint64_t)max_rows};
     const uint64_t sa[1] = {(uint64_t)g.lda * 2};
     const uint32_t ba[2] = {64, 128u};
     // with the gather fused, A is read by the gather warps: no map of it is needed
     if (!gather) ok = ok && make_map(&tmA, g.A, 2, da, sa, ba);
-    if (MODE == kFwd) {
+    if (MODE == kFwd && b_wide) {
+      const uint64_t db[4] = {64, (uint64_t)g.K, (uint64_t)g.N / 64, (uint64_t)g.E};
+      const uint64_t sb[3] = {(uint64_t)g.ldb * 2, 128, (uint64_t)g.b_expert_stride * 2};
+      const uint32_t bb[4] = {64, 64, BN / 64, 1};
+      ok = ok && make_map(&tmB, g.B, 4, db, sb, bb);
+    } else if (MODE == kFwd) {
       const uint64_t db[3] = {(uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.E};
       const uint64_t sb[2] = {(uint64_t)g.ldb * 2, (uint64_t)g.b_expert_stride * 2};
       const uint32_t bb[3] = {64, 64, 1};
@@ -853,7 +915,20 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
   }
   if (!ok) return YAMOE_ERR_CUDA;
   if (gather) tmA = tmB;              // placeholder for the unused kernel parameter
-  auto kern = umma_gemm_kernel<MODE, BN, Epi>;
+  if constexpr (MODE == kFwd && epi_gathers<Epi>::value) {
+    if (gather) return launch_umma_kernel<MODE, BN, Epi, true>(g, epi, tmA, tmB, max_tiles, a_wide, b_wide, stream);
+  } else {
+    if (gather) return YAMOE_ERR_UNSUPPORTED;     // no gathering instantiation for this epilogue
+  }
+  return launch_umma_kernel<MODE, BN, Epi, false>(g, epi, tmA, tmB, max_tiles, a_wide, b_wide, stream);
+}
+
+template <int MODE, int BN, class Epi, bool GATHER>
+inline int launch_umma_kernel(const GemmArgs& g, const Epi& epi, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                              int64_t max_tiles, bool a_wide, bool b_wide, cudaStream_t stream) {
+  using SM = UmmaSmem<BN>;
+  constexpr bool gather = GATHER;
+  auto kern = umma_gemm_kernel<MODE, BN, Epi, GATHER>;
   static PerDevice<int> attr_done;   // per template instantiation and device
   const int dev = current_device_index();
   if (!attr_done.get(dev)) {
@@ -862,7 +937,7 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
     attr_done.set(dev, 1);
   }
   UmmaParams p{g.M, g.N, g.K, g.E, g.tile_expert, g.pad_off, (int)max_tiles, const_cast<int32_t*>(g.header),
-               gather ? g.gather_rows : nullptr, g.A, g.lda, g.gate};
+               gather ? g.gather_rows : nullptr, g.A, g.lda, g.gate, a_wide ? 1 : 0, b_wide ? 1 : 0};
   const int NT = (int)ceil_div(g.N, BN);
   int64_t total_max = MODE == kWgrad ? (int64_t)g.E * ceil_div(g.M, kUmmaBM) * NT : max_tiles * NT;
   int grid = (int)std::min<int64_t>(total_max, umma_sm_count());

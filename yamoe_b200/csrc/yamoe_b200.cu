@@ -159,15 +159,15 @@ static int prepare_routing(const Plan& p, cudaStream_t st) {
   return YAMOE_OK;
 }
 
-// The gate_up GEMM of the forward fetches its A rows straight from hidden_states (four extra warps
-// per CTA copy them into the swizzled A stage with cp.async), so that the permuted activations are
-// never written to global memory.  Measured equal to the separate gather kernel plus a TMA-fed GEMM
-// (0.868 against 0.867 ms per forward at T = 4096: the GEMM itself 532 against 505 us, the 27 us
-// gather kernel gone).  YAMOE_B200_FUSED_GATHER=0 selects the separate kernel.
+// YAMOE_B200_FUSED_GATHER=1 lets the gate_up GEMM of the forward fetch its A rows straight from
+// hidden_states (four extra warps per CTA copy them into the swizzled A stage with cp.async), so
+// that the permuted activations are never written to global memory.  Off by default: the GEMM fed
+// that way measures 518 us against 457 us for the TMA-fed one, more than the 27 us gather kernel
+// it saves (0.841 against 0.814 ms per forward at T = 4096).
 static bool fused_gather_enabled() {
   static int on = []() {
     const char* env = std::getenv("YAMOE_B200_FUSED_GATHER");
-    return env ? std::atoi(env) : 1;
+    return env ? std::atoi(env) : 0;
   }();
   return on != 0;
 }
