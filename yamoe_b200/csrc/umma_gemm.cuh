@@ -870,12 +870,14 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
     const char* env = std::getenv("YAMOE_B200_WIDE_TMA");
     return env == nullptr || std::atoi(env) != 0;
   }();
-  const bool a_wide = wide_on && MODE == kWgrad && g.M % 64 == 0;
-  const bool b_wide = wide_on && MODE != kDgrad && g.N % 64 == 0;
+  // (weight gradient: the operands' row pitch decides - columns between the width and the pitch
+  // exist in memory, and whatever they hold only reaches output rows / columns that are not stored)
+  const bool a_wide = wide_on && MODE == kWgrad && g.lda % 64 == 0 && g.M <= g.lda;
+  const bool b_wide = wide_on && (MODE == kWgrad ? (g.ldb % 64 == 0 && g.N <= g.ldb) : (MODE == kFwd && g.N % 64 == 0));
   if (MODE == kWgrad) {
     const uint32_t ba[2] = {64, 64};
     if (a_wide) {
-      const uint64_t da[3] = {64, (uint64_t)max_rows, (uint64_t)g.M / 64}, sa[2] = {(uint64_t)g.lda * 2, 128};
+      const uint64_t da[3] = {64, (uint64_t)max_rows, (uint64_t)g.lda / 64}, sa[2] = {(uint64_t)g.lda * 2, 128};
       const uint32_t bw[3] = {64, 64, kUmmaBM / 64};
       ok = ok && make_map(&tmA, g.A, 3, da, sa, bw);
     } else {
@@ -883,7 +885,7 @@ inline int launch_umma_gemm_bn(const GemmArgs& g, const Epi& epi, int64_t max_ro
       ok = ok && make_map(&tmA, g.A, 2, da, sa, ba);
     }
     if (b_wide) {
-      const uint64_t db[3] = {64, (uint64_t)max_rows, (uint64_t)g.N / 64}, sb[2] = {(uint64_t)g.ldb * 2, 128};
+      const uint64_t db[3] = {64, (uint64_t)max_rows, (uint64_t)g.ldb / 64}, sb[2] = {(uint64_t)g.ldb * 2, 128};
       const uint32_t bw[3] = {64, 64, BN / 64};
       ok = ok && make_map(&tmB, g.B, 3, db, sb, bw);
     } else {
