@@ -740,9 +740,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
   // A gated kernel ran next to its predecessor; it ends only once that kernel has ended, so that
   // "this kernel is complete" keeps implying "everything before it on the stream is complete".
-#ifndef YB_NO_END_WAIT
   if (gated) pdl_wait();
-#endif
 }
 
 // ---------------------------------------------------------------------------------------------
