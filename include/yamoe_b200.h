@@ -282,10 +282,12 @@ int yamoe_b200_router_topk(const void *router_logits, int64_t *router_indices, v
  * F.linear -> topk -> softmax -> zeros_like().scatter_() of Yamoe.forward
  * (torch-ext/yamoe/layers.py:126-149; oracle torch-ext/yamoe/vendored/gpt_oss_mlp.py:119-139):
  *   logits = hidden_states [T,H] @ router_weight [E,H]^T + router_bias [E]   (rounded to `dtype`)
- * followed by what yamoe_b200_router_topk does.  For bf16 with H a multiple of 64 and E <= 256 this is
- * ONE kernel (a tcgen05 GEMM whose epilogue does the top-k, softmax and scatter); otherwise the
- * CUDA-core GEMM and the top-k kernel run back to back.  router_bias may be NULL.  The workspace
- * (256-byte aligned, yamoe_b200_router_workspace_bytes) holds the logits and a status header. */
+ * followed by what yamoe_b200_router_topk does.  ONE kernel in two cases: up to 64 tokens (either
+ * dtype; a warp per (token, expert) dot product, the CTA finishing a token last selects), and bf16
+ * with H a multiple of 64, E <= 256 and K <= 8 (a tcgen05 GEMM whose epilogue does the top-k,
+ * softmax and scatter).  Otherwise a GEMM and the top-k kernel run back to back.  router_bias may
+ * be NULL.  The workspace (256-byte aligned, yamoe_b200_router_workspace_bytes) holds a status
+ * header, per-token tickets and the logits or the selection state. */
 size_t yamoe_b200_router_workspace_bytes(int64_t T, int E);
 int yamoe_b200_router_forward(const void *hidden_states, const void *router_weight, const void *router_bias,
                               int64_t *router_indices, void *router_scores, int64_t T, int H, int E, int K,
